@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define LCC_ABI_VERSION 9
+#define LCC_ABI_VERSION 10
 #define LCC_PAGE_SIZE 64
 
 typedef struct lcc_ctx lcc_ctx;
@@ -305,11 +305,26 @@ int lcc_resize_bicubic_aa_u8(lcc_ctx* ctx, const lcc_resize_plan* plan, const ui
 #define LCC_MIX_PARALLEL 2 /* chunk-local sink attention (left) beside gated linear attention (right), averaged after a norm each */
 #define LCC_MIX_RETENTION 3 /* rotary q/k -> linear attention with a fixed decay per head, no normaliser -> unit-rms heads x silu gate -> out-proj */
 #define LCC_MIX_LATENT 4    /* causal softmax attention over a cached low-rank latent + one shared rotary key part, per-head sink and sigmoid gate */
+#define LCC_MIX_ATTENTION 5 /* softmax attention over paged K/V: per-head q/k RMS norm, rotary positions on part of a head, a sliding
+                               window and / or chunks, optional sink, values projected or taken from the keys as projected, output
+                               gate per head or per channel (every option a field of the layer) */
 #define LCC_FF_GLU 0        /* dense gated feed-forward: gelu_tanh(gate) * up */
-#define LCC_FF_MOE 1        /* routed experts (sigmoid router, top-k of score + correction, relu^2 experts) + gated shared expert */
+#define LCC_FF_MOE 1        /* routed experts (sigmoid or softmax router, top-k of score + correction, optionally inside the best groups
+                               of neighbouring experts; relu^2 or clamped gated experts; identity experts) + gated shared expert */
+#define LCC_FF_MLP 2        /* dense two-matrix feed-forward: down(gelu_tanh(up x)) */
 #define LCC_BLOCK_POSTNORM 0 /* x <- norm(alpha * x + sublayer(x)) */
 #define LCC_BLOCK_PRENORM_HC 1 /* `streams` residual streams x_s; per sublayer: u = sum_s in[s] x_s; y = sublayer(norm(u));
                                   x_t <- sum_s mix[s][t] x_s + out[t] y. The model's output is the sum of the streams. */
+#define LCC_BLOCK_PARALLEL 2   /* h = norm1(x); x <- x + mixer(h) + ff(h): one norm, both sublayers read it, one fp32 residual sum */
+#define LCC_NORM_RMS 0         /* x / sqrt(mean(x^2) + eps) * w */
+#define LCC_NORM_DYT 1         /* tanh(alpha * x) * w + b: no statistics of the row (Dynamic Tanh) */
+#define LCC_ROUTER_SIGMOID 0
+#define LCC_ROUTER_SOFTMAX 1   /* scores = softmax over all router outputs (identity experts included) */
+#define LCC_EXPERT_RELU2 0     /* down(relu(up x)^2) */
+#define LCC_EXPERT_CLAMP_GLU 1 /* g = min(gate x, limit), u = clamp(up x, +-limit); down(g * sigmoid(1.702 g) * (u + 1)); e_up rows [gate | up] */
+#define LCC_GATE_NONE 0
+#define LCC_GATE_HEAD 1        /* one sigmoid gate per (row, head) */
+#define LCC_GATE_CHANNEL 2     /* one sigmoid gate per (row, head, value channel) */
 
 typedef struct {
     int32_t type; /* LCC_MIX_* */
@@ -330,12 +345,29 @@ typedef struct {
     int32_t a_heads, a_dim, a_rot_dim, a_vdim, a_rank, a_kv_from;
     float a_scale;
     float rot_mag;  /* factor on cos and sin of the rotation (1 without long-context scaling) */
+    /* LCC_MIX_ATTENTION: m_heads query heads over m_kv_heads key/value heads; per-head RMS norm of q and k (weights [m_dim], shared by
+     * the heads); the first m_rot_dims channels of a head rotated (m_rot_pairs: channel 2i with 2i+1, else i with i + dims/2);
+     * a row at position i sees j <= i with i - j < m_window (m_window <= 0: no window) inside its chunk of m_chunk positions
+     * (<= 0: none); m_sink: a zero-logit sink in the softmax denominator; m_value_keys: the values are the keys as projected
+     * (before norm and rotation; the layer has no value projection); m_gate: LCC_GATE_* */
+    int32_t m_heads, m_kv_heads, m_dim, m_vdim, m_window, m_chunk, m_rot_dims, m_rot_pairs, m_sink, m_value_keys, m_gate;
+    float m_scale;
     /* feed-forward: ff_kind LCC_FF_*; MoE: e_experts experts of width e_ff, e_top per token, weights = score * e_scale,
      * shared expert of width e_shared_ff (0 = none) */
     int32_t ff_kind, e_experts, e_top, e_ff, e_shared_ff;
     float e_scale;
+    /* e_router_kind LCC_ROUTER_*; the last e_identity router outputs (beyond the e_experts real ones) stand for experts that return
+     * their input; e_groups > 0: the router outputs form e_groups equal groups of neighbours and only the e_keep groups with the
+     * largest choice score can be chosen; e_act LCC_EXPERT_*, e_limit its clamp */
+    int32_t e_router_kind, e_identity, e_groups, e_keep, e_act;
+    float e_limit;
+    float norm1_alpha; /* LCC_NORM_DYT: the scalar inside tanh */
     /* weights: matrices [out, in] in the model's storage type; everything named *_f32 is fp32 */
     const float *norm1_f32, *norm2_f32;
+    const float* norm1_bias_f32; /* LCC_NORM_DYT: [width] */
+    const void* m_in;          /* [Hq*dim + G*dim (+ G*vdim) + gate rows, width], rows [q | k | (v) | gate] */
+    const float *m_qnorm_f32, *m_knorm_f32; /* [dim] each */
+    const void* m_out;         /* [width, Hq*vdim] */
     const void* s_in;          /* [2*inner + 2*groups*state + heads, width], rows [z | x | B | C | dt] */
     const float *s_conv_w_f32, *s_conv_b_f32; /* [inner + 2*groups*state, conv], [..] */
     const float *s_dt_bias_f32, *s_a_log_f32, *s_skip_f32, *s_norm_f32; /* [heads] x3, [inner] */
@@ -352,7 +384,7 @@ typedef struct {
     const float* r_norm_f32;   /* [vdim], shared by the heads */
     const void* r_out;         /* [width, heads*vdim] */
     const float* r_branch_norm_f32; /* [width] */
-    const void* ff_in;         /* [2*ff, width], rows [gate | up]; act = gelu_tanh(gate) * up */
+    const void* ff_in;         /* LCC_FF_GLU: [2*ff, width], rows [gate | up]; act = gelu_tanh(gate) * up. LCC_FF_MLP: [ff, width] */
     const void* ff_out;        /* [width, ff] */
     const float* rot_inv_freq_f32; /* [rot dims / 2]: rotation frequencies of this layer's mixer, computed by the host */
     const void* t_in;          /* [2*heads*dim + 2*heads*vdim, width], rows [q | k | v | gate] */
@@ -366,9 +398,9 @@ typedef struct {
     const void* a_uv;          /* [heads*vdim, rank] */
     const float* a_sink_f32;   /* [heads] sink logits */
     const void* a_out;         /* [width, heads*vdim] */
-    const void* e_router;      /* [experts (+1), width]: router rows, then the shared expert's gate row */
-    const float* e_correction_f32; /* [experts]: added to the scores for the choice only */
-    const void* e_up;          /* [experts][e_ff, width] */
+    const void* e_router;      /* [experts + identity (+1), width]: router rows, then the shared expert's gate row */
+    const float* e_correction_f32; /* [experts + identity]: added to the scores for the choice only */
+    const void* e_up;          /* [experts][e_ff, width]; LCC_EXPERT_CLAMP_GLU: [experts][2*e_ff, width], rows [gate | up] */
     const void* e_down;        /* [experts][width, e_ff] */
     const void* e_shared_up;   /* [e_shared_ff, width] */
     const void* e_shared_down; /* [width, e_shared_ff] */
@@ -382,6 +414,10 @@ typedef struct {
     float eps, alpha, embed_scale, logit_softcap; /* logit_softcap <= 0: none */
     int32_t block;   /* LCC_BLOCK_* */
     int32_t streams; /* residual streams of LCC_BLOCK_PRENORM_HC (>= 1) */
+    int32_t norm_kind; /* LCC_NORM_*: the block norms and the final norm */
+    float final_norm_alpha; /* LCC_NORM_DYT */
+    float logit_scale;      /* logits are multiplied by it (0 reads as 1) */
+    const float* final_norm_bias_f32; /* LCC_NORM_DYT: [width] */
     const void* embed;          /* [vocab, width] */
     const float* inv_freq_f32;  /* [width/2]: sinusoidal position frequencies, computed by the host; NULL: the embedding has no position term */
     const float* final_norm_f32;

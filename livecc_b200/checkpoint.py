@@ -319,10 +319,18 @@ def seq_param_specs(cfg) -> List[Tuple[str, Tuple[int, ...], str]]:
     specs = [("embed", (cfg.vocab, W), "embed")]
     hc = getattr(cfg, "block", "postnorm") == "prenorm_hc"
     norm = "norm0" if getattr(cfg, "norm_offset", 0.0) else "norm"   # weights stored around zero
+    par = getattr(cfg, "block", "postnorm") == "parallel"     # one norm per layer
+    dyt = getattr(cfg, "norm", "rms") == "dyt"                # a norm is a weight, a bias and a scalar
+
+    def norm_specs(name):
+        return [(name, (W,), norm)] + ([(name + ".b", (W,), "b"), (name + ".alpha", (), "alpha")] if dyt else [])
+
     for i, L in enumerate(cfg.layers):
+        if getattr(L, "weights_of", -1) >= 0:                 # runs with another layer's tensors
+            continue
         p = f"l{i}."
-        specs.append((p + "norm1", (W,), norm))
-        if L.ff or L.moe:
+        specs += norm_specs(p + "norm1")
+        if (L.ff or L.moe) and not par:
             specs.append((p + "norm2", (W,), norm))
         if hc:
             n = cfg.streams
@@ -339,6 +347,15 @@ def seq_param_specs(cfg) -> List[Tuple[str, Tuple[int, ...], str]]:
                 specs += [(m + "dkv", (a.kv_rank + a.rot_dim, W), "w"), (m + "dkv.norm", (a.kv_rank,), "norm")]
             specs += [(m + "uk", (a.heads * a.dim, a.kv_rank), "w"), (m + "uv", (a.heads * a.vdim, a.kv_rank), "w"),
                       (m + "sink", (a.heads,), "skip"), (m + "g", (a.heads, W), "w"), (m + "o", (W, a.heads * a.vdim), "w")]
+        elif L.type == "attention":
+            a, m = L.attn, p + "mix."
+            specs += [(m + "q", (a.heads * a.dim, W), "w"), (m + "k", (a.kv_heads * a.dim, W), "w"),
+                      (m + "q.norm", (a.dim,), "norm"), (m + "k.norm", (a.dim,), "norm")]
+            if not a.value_keys:
+                specs.append((m + "v", (a.kv_heads * a.vdim, W), "w"))
+            if a.gate != "none":
+                specs.append((m + "g", (a.gate_rows, W), "w"))
+            specs.append((m + "o", (W, a.heads * a.vdim), "w"))
         elif L.type == "mamba2":
             s, m = L.ssd, p + "mix."
             specs += [(m + "in", (s.proj_rows, W), "w"), (m + "conv", (s.conv_channels, s.conv), "conv"),
@@ -361,14 +378,18 @@ def seq_param_specs(cfg) -> List[Tuple[str, Tuple[int, ...], str]]:
         if L.moe:
             e, m = L.moe, p + "mlp."
             for j in range(e.experts):
+                if e.act == "clamp_glu":
+                    specs.append((f"{m}e{j}.gate", (e.ff, W), "w"))
                 specs += [(f"{m}e{j}.up", (e.ff, W), "w"), (f"{m}e{j}.down", (W, e.ff), "w")]
-            specs += [(m + "router", (e.experts, W), "w"), (m + "correction", (e.experts,), "b")]
+            specs += [(m + "router", (e.outputs, W), "w"), (m + "correction", (e.outputs,), "b")]
             if e.shared_ff:
                 specs += [(m + "shared.up", (e.shared_ff, W), "w"), (m + "shared.down", (W, e.shared_ff), "w"),
                           (m + "shared.sg", (1, W), "w")]
         elif L.ff:
-            specs += [(p + "mlp.gate", (L.ff, W), "w"), (p + "mlp.up", (L.ff, W), "w"), (p + "mlp.down", (W, L.ff), "w")]
-    specs += [("final.norm", (W,), norm), ("head", (cfg.vocab, W), "w")]
+            if getattr(cfg, "dense", "glu") != "mlp":
+                specs.append((p + "mlp.gate", (L.ff, W), "w"))
+            specs += [(p + "mlp.up", (L.ff, W), "w"), (p + "mlp.down", (W, L.ff), "w")]
+    specs += norm_specs("final.norm") + [("head", (cfg.vocab, W), "w")]
     return specs
 
 
@@ -390,6 +411,8 @@ def synthetic_seq_tensors(cfg, seed: int = 1234, device="cpu") -> Dict[str, torc
             t = 1.0 + 0.5 * u
         elif kind == "norm0":
             t = 0.5 * u
+        elif kind == "alpha":
+            t = 0.75 + 0.5 * u
         elif kind == "hc_in":
             t = (1.0 + u) / shape[0]
         elif kind == "hc_out":

@@ -244,13 +244,53 @@ class LatentAttnConfig:
 
 @dataclass
 class MoeConfig:
-    """Routed feed-forward: `experts` relu^2 experts of width `ff`, `top` per token chosen by sigmoid score + correction,
-    weighted by score * scale; a shared expert of width `shared_ff` (0: none) behind a scalar sigmoid gate."""
+    """Routed feed-forward: `experts` experts of width `ff`, `top` per token chosen by score + correction, weighted by
+    score * scale (never renormalised); a shared expert of width `shared_ff` (0: none) behind a scalar sigmoid gate.
+    `router`: "sigmoid" (a score per expert) or "softmax" (over all router outputs). The last `identity` router outputs
+    (beyond `experts`) stand for experts that return their input. `groups` > 0: the router outputs form that many equal
+    groups of neighbours, a group scores as its best choice score, and only members of the best `keep` groups can be chosen.
+    `act`: "relu2" (down(relu(up x)^2)) or "clamp_glu" (g = min(gate x, limit), u = clamp(up x, -limit, limit),
+    down(g sigmoid(1.702 g) (u + 1)))."""
     experts: int
     top: int
     ff: int
     scale: float = 1.0
     shared_ff: int = 0
+    router: str = "sigmoid"
+    identity: int = 0
+    groups: int = 0
+    keep: int = 0
+    act: str = "relu2"
+    limit: float = 0.0
+
+    @property
+    def outputs(self) -> int:
+        """Rows of the router matrix."""
+        return self.experts + self.identity
+
+
+@dataclass
+class MaskedAttnConfig:
+    """Softmax attention over paged keys and values with per-head q/k RMS norm (one weight of `dim` channels shared by the
+    heads), rotary positions on the first rot.dims channels of a head (`rot_pairs`: channel 2i turns with 2i+1, else i with
+    i + dims/2), a sliding window (row i sees j with 0 <= i - j < window; 0: none), `value_keys`: the values are the keys
+    as projected, before norm and rotation (no value projection), `gate`: "none", "head" or "channel" (sigmoid of a
+    projection of the mixer's input, applied before the output projection), `sink`: a zero-logit term in the denominator."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    window: int
+    scale: float
+    rot: RotaryConfig
+    rot_pairs: bool = True
+    value_keys: bool = True
+    gate: str = "channel"
+    sink: bool = False
+
+    @property
+    def gate_rows(self) -> int:
+        return {"none": 0, "head": self.heads, "channel": self.heads * self.vdim}[self.gate]
 
 
 @dataclass
@@ -263,6 +303,8 @@ class SeqLayerConfig:
     retention: RetentionConfig = None
     latent: LatentAttnConfig = None
     moe: MoeConfig = None          # routed feed-forward instead of the dense one
+    attn: MaskedAttnConfig = None  # type "attention"
+    weights_of: int = -1           # >= 0: the layer owns no tensors and runs with that layer's (cache and state are its own)
 
 
 # What an architecture name fixes (everything else comes from config.json): the residual block form, whether the stored
@@ -270,6 +312,10 @@ class SeqLayerConfig:
 SEQ_FAMILIES = {
     "Bimopel": dict(block="postnorm", norm_offset=0.0, positions="sinusoid"),
     "Kedelorn": dict(block="prenorm_hc", norm_offset=1.0, positions=None),
+    # parallel blocks behind one Dynamic-Tanh norm; attention whose values are the un-normed keys, pair-interleaved rotary
+    # positions, a gate per channel; two-matrix gelu feed-forward; softmax router, clamped gated experts
+    "Dibedra": dict(block="parallel", norm_offset=0.0, positions=None, norm="dyt", dense="mlp", router="softmax", expert="clamp_glu",
+                    attention=dict(rot_pairs=True, value_keys=True, gate="channel", sink=False)),
 }
 
 
@@ -284,7 +330,10 @@ class SeqModelConfig:
     embed_scale: float = 1.0
     logit_softcap: float = 0.0
     eos_token_id: int = -1         # none unless config.json names one
-    block: str = "postnorm"        # "postnorm" | "prenorm_hc" (pre-norm sublayers on `streams` residual streams)
+    block: str = "postnorm"        # "postnorm" | "prenorm_hc" (pre-norm sublayers on `streams` residual streams) | "parallel"
+    norm: str = "rms"              # "rms" | "dyt" (tanh(alpha x) w + b; tensors <name>, <name>.b, <name>.alpha)
+    dense: str = "glu"             # dense feed-forward: "glu" (gelu_tanh(gate) * up) | "mlp" (gelu_tanh(up))
+    logit_scale: float = 1.0
     streams: int = 1
     norm_offset: float = 0.0       # added to every stored layer-norm weight (1.0: weights stored around zero)
     positions: str = "sinusoid"    # position term of the embedding, or None
@@ -305,12 +354,28 @@ class SeqModelConfig:
                 if kind == "dense":
                     ff = int(mlp["ff"])
                 elif kind == "moe":
-                    r, sh = mlp["router"], mlp.get("shared")
+                    r, sh, gr = mlp["router"], mlp.get("shared"), mlp["router"].get("groups")
                     moe = MoeConfig(experts=int(r["experts"]), top=int(r["top"]), ff=int(mlp["expert"]["ff"]),
-                                    scale=float(r.get("scale", 1.0)), shared_ff=int(sh["ff"]) if sh else 0)
+                                    scale=float(r.get("scale", 1.0)), shared_ff=int(sh["ff"]) if sh else 0,
+                                    router=fam.get("router", "sigmoid"), identity=int(r.get("identity", 0)),
+                                    groups=int(gr["count"]) if gr else 0, keep=int(gr["keep"]) if gr else 0,
+                                    act=fam.get("expert", "relu2"), limit=float(mlp["expert"].get("limit", 0.0)))
                 else:
                     raise NotImplementedError(f"layer {i}: feed-forward kind {kind!r} is not supported")
-            if L["type"] == "retention":
+            share = L.get("weights_of")
+            if share is not None:
+                share = int(share)
+                if not 0 <= share < i or d["layers"][share].get("weights_of") is not None:
+                    raise ValueError(f"layer {i}: weights_of must name an earlier layer that owns its tensors")
+            if L["type"] == "attention":
+                if "attention" not in fam:
+                    raise NotImplementedError(f"layer {i}: {arch} has no mixer of type 'attention'")
+                rot = RotaryConfig.from_json(mx["rot"]) if mx.get("rot") else RotaryConfig(0, 10000.0)
+                layers.append(SeqLayerConfig("attention", ff=ff, moe=moe, weights_of=-1 if share is None else share, attn=MaskedAttnConfig(
+                    heads=int(mx["heads"]), kv_heads=int(mx.get("kv_heads", mx["heads"])), dim=int(mx["dim"]),
+                    vdim=int(mx.get("vdim", mx["dim"])), window=int((mx.get("mask") or {}).get("size", 0)),
+                    scale=float(mx.get("scale", float(mx["dim"]) ** -0.5)), rot=rot, **fam["attention"])))
+            elif L["type"] == "retention":
                 rot = RotaryConfig.from_json(mx["rot"]) if mx.get("rot") else RotaryConfig(0, 10000.0)
                 layers.append(SeqLayerConfig("retention", ff=ff, moe=moe, retention=RetentionConfig(
                     heads=int(mx["heads"]), dim=int(mx["dim"]), vdim=int(mx.get("vdim", mx["dim"])),
@@ -340,7 +405,8 @@ class SeqModelConfig:
             eps=float((d.get("norm") or {}).get("eps", 1e-5)), alpha=float(d.get("postln_alpha", 1.0)),
             embed_scale=float((d.get("embedding") or {}).get("scale", 1.0)), logit_softcap=float(d.get("logit_softcap") or 0.0),
             eos_token_id=int(d.get("eos_token_id", -1)), block=fam["block"], streams=int(d.get("streams", 1)),
-            norm_offset=fam["norm_offset"], positions=fam["positions"])
+            norm_offset=fam["norm_offset"], positions=fam["positions"], norm=fam.get("norm", "rms"), dense=fam.get("dense", "glu"),
+            logit_scale=float(d.get("logit_scale", 1.0)))
 
     def to_json(self) -> dict:
         """The inverse of from_json (used to write synthetic checkpoints)."""
@@ -357,6 +423,11 @@ class SeqModelConfig:
                 mx = dict(heads=a.heads, dim=a.dim, rot_dim=a.rot_dim, vdim=a.vdim, kv_rank=a.kv_rank, scale=a.scale, rot=a.rot.to_json())
                 if a.kv_from >= 0:
                     mx["kv_from"] = a.kv_from
+            elif L.type == "attention":
+                a = L.attn
+                mx = dict(heads=a.heads, kv_heads=a.kv_heads, dim=a.dim, vdim=a.vdim, scale=a.scale, rot=a.rot.to_json())
+                if a.window:
+                    mx["mask"] = dict(size=a.window)
             else:
                 l, r = L.left, L.right
                 mx = dict(left=dict(heads=l.heads, kv_heads=l.kv_heads, dim=l.dim, vdim=l.vdim, mask=dict(size=l.chunk), scale=l.scale),
@@ -367,7 +438,19 @@ class SeqModelConfig:
                 mlp = dict(kind="moe", expert=dict(ff=e.ff), router=dict(experts=e.experts, top=e.top, scale=e.scale))
                 if e.shared_ff:
                     mlp["shared"] = dict(ff=e.shared_ff)
+                if e.act == "clamp_glu":
+                    mlp["expert"]["limit"] = e.limit
+                    del mlp["router"]["scale"]
+                if e.identity:
+                    mlp["router"]["identity"] = e.identity
+                if e.groups:
+                    mlp["router"]["groups"] = dict(count=e.groups, keep=e.keep)
             out.append(dict(type=L.type, mixer=mx, mlp=mlp))
+            if L.weights_of >= 0:
+                out[-1]["weights_of"] = L.weights_of
+        if self.block == "parallel":
+            return dict(architecture=self.architecture, vocab=self.vocab, width=self.width, layers=out, norm=dict(eps=self.eps),
+                        logit_scale=self.logit_scale)
         if self.block == "prenorm_hc":
             return dict(architecture=self.architecture, vocab=self.vocab, width=self.width, streams=self.streams, layers=out,
                         norm=dict(eps=self.eps))
@@ -380,8 +463,23 @@ class SeqModelConfig:
         if self.block == "prenorm_hc" and not 1 <= self.streams <= 8:
             raise ValueError("1 to 8 residual streams")
         for i, L in enumerate(self.layers):
-            if L.moe and not (1 <= L.moe.top <= L.moe.experts <= 512):
+            if L.moe and not (1 <= L.moe.top <= L.moe.outputs <= 512 and L.moe.experts >= 1 and L.moe.identity >= 0):
                 raise ValueError(f"layer {i}: unsupported router sizes {L.moe}")
+            if L.moe and L.moe.groups and (L.moe.outputs % L.moe.groups or not 1 <= L.moe.keep <= L.moe.groups or
+                                           L.moe.keep * (L.moe.outputs // L.moe.groups) < L.moe.top):
+                raise ValueError(f"layer {i}: the kept groups must be equal groups that hold at least `top` experts: {L.moe}")
+            if L.moe and (L.moe.identity or L.moe.act == "clamp_glu") and L.moe.shared_ff:
+                raise ValueError(f"layer {i}: identity experts and a shared expert do not combine")
+            if L.weights_of >= 0 and self.block != "parallel":
+                raise ValueError(f"layer {i}: shared layer weights are served in parallel blocks only")
+            if L.type == "attention":
+                a = L.attn
+                if self.block != "parallel":
+                    raise ValueError(f"layer {i}: the attention mixer is served in parallel blocks")
+                if a.heads < 1 or a.kv_heads < 1 or a.heads % a.kv_heads or a.dim < 1 or a.window < 0 or a.rot.dims % 2 or \
+                        a.rot.dims > a.dim or (a.value_keys and a.vdim != a.dim):
+                    raise ValueError(f"layer {i}: unsupported attention sizes {a}")
+                continue
             if L.type == "mamba2":
                 s = L.ssd
                 if s.heads % s.groups or s.inner % s.norm_groups or not 1 <= s.conv <= 8 or s.state > 512:

@@ -2,6 +2,7 @@
 //   * q/k RMS norm over the whole projection (all heads at once) and the append of k, v to the pages,
 //   * attention of new rows over the keys of their own chunk (chunks counted from position 0 of the sequence) with a
 //     softmax sink: p_j = exp(s_j) / (exp(sink_h) + sum_j exp(s_j)) (sink_h = 0 unless given), and a per-head sigmoid output gate.
+// Options (AttnOpts): a sliding window instead of / inside the chunks, no sink (ordinary softmax), one gate per output channel.
 // Scores, weights and the accumulation are fp32; K and V pages hold the model's storage type.
 #include <math.h>
 #include <stdlib.h>
@@ -25,6 +26,74 @@ template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = _
 
 __device__ __forceinline__ int seq_past(const SeqPos& p, int) { return p.kv_len ? *p.kv_len : p.past; }
 __device__ __forceinline__ bool seq_done(const SeqPos& p) { return p.finished && *p.finished; }
+
+// first key a row at position p sees: the start of its chunk, and / or p - window + 1
+__device__ __forceinline__ int first_key(int p, int chunk, int window) {
+    int lo = chunk > 0 ? (p / chunk) * chunk : 0;
+    if (window > 0) lo = max(lo, p - window + 1);
+    return lo;
+}
+// A softmax without a sink starts its running (max, sum) at (kNoSinkMax, 0): finite, so that a tile in which a row sees no
+// key leaves both unchanged (exp(-inf - kNoSinkMax) = 0) and the first visible key rescales the empty sum by exp(-huge) = 0.
+constexpr float kNoSinkMax = -1e30f;
+// sigmoid gate of output element (row t, head h, channel c): one per head, or one per channel
+template <typename T>
+__device__ __forceinline__ float gate_of(const T* gate, int ld_gate, int t, int h, int c, int DV, bool per_channel) {
+    const float z = ldf(gate + (size_t)t * ld_gate + (per_channel ? (size_t)h * DV + c : (size_t)h));
+    return 1.f / (1.f + expf(-z));
+}
+
+// One CTA per new row, one warp per head in turn (query heads, then key heads). Per head: sum of squares over D -> the
+// normed channels -> rotation of the first rot_dims channels -> q_out, or the K page; the V page takes its columns of the
+// row as they are.
+template <typename T>
+__global__ void __launch_bounds__(256) qk_headnorm_rope_append_kernel(const T* __restrict__ proj, int ld, int v_col,
+                                                                      const float* __restrict__ qn_w, const float* __restrict__ kn_w,
+                                                                      float eps, const float* __restrict__ inv_freq, float mag,
+                                                                      int rot_dims, int rot_pairs, float* __restrict__ q_out,
+                                                                      T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                                                      const int* __restrict__ page_table, int page_size, int S, int Hq,
+                                                                      int G, int D, int DV, SeqPos pos) {
+    if (seq_done(pos)) return;
+    const int t = blockIdx.x;
+    const int p = seq_past(pos, S) + t;
+    const float pf = (float)p;
+    const T* row = proj + (size_t)t * ld;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int page = page_table[p / page_size], slot = p % page_size;
+    const int half = rot_dims >> 1;
+    for (int hd = warp; hd < Hq + G; hd += nwarps) {
+        const bool is_q = hd < Hq;
+        const T* x = row + (size_t)hd * D;                 // k heads follow the q heads in the row
+        const float* w = is_q ? qn_w : kn_w;
+        float ss = 0.f;
+        for (int c = lane; c < D; c += 32) { const float v = ldf(x + c); ss = fmaf(v, v, ss); }
+        ss = warp_sum(ss);
+        const float rn = w ? 1.f / sqrtf(ss / (float)D + eps) : 1.f;
+        for (int c = lane; c < D; c += 32) {
+            float v = ldf(x + c) * rn * (w ? w[c] : 1.f);
+            if (c < rot_dims) {
+                // the pair (u, v) becomes (u cos - v sin, v cos + u sin): `first` tells which member this channel is
+                const bool first = rot_pairs ? !(c & 1) : c < half;
+                const int i = rot_pairs ? (c >> 1) : (first ? c : c - half);
+                const int pc = rot_pairs ? (c ^ 1) : (first ? c + half : c - half);
+                const float o = ldf(x + pc) * rn * (w ? w[pc] : 1.f);
+                const float ang = pf * inv_freq[i];
+                float sn, cs;
+                sincosf(ang, &sn, &cs);
+                sn *= mag; cs *= mag;
+                v = first ? v * cs - o * sn : v * cs + o * sn;
+            }
+            if (is_q) q_out[((size_t)t * Hq + hd) * D + c] = v;
+            else stf(k_pages + (((size_t)page * G + (hd - Hq)) * page_size + slot) * D + c, v);
+        }
+    }
+    const int nv = G * DV;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+        const int g = i / DV, d = i % DV;
+        v_pages[(((size_t)page * G + g) * page_size + slot) * DV + d] = row[v_col + i];
+    }
+}
 
 // One CTA per new row.
 template <typename T>
@@ -65,15 +134,15 @@ __global__ void __launch_bounds__(128) attn_chunk_sink_kernel(const float* __res
                                                               int page_size, const T* __restrict__ gate, int ld_gate,
                                                               T* __restrict__ out, int ld_out, int S, int Hq, int G, int D, int DV,
                                                               int chunk, float scale, SeqPos pos,
-                                                              const float* __restrict__ sink, int ld_v) {
+                                                              const float* __restrict__ sink, int ld_v, AttnOpts opt) {
     if (seq_done(pos)) return;
     extern __shared__ float sm[];
     __shared__ float red[32];
     const int t = blockIdx.x, h = blockIdx.y;
-    const float sk = sink ? sink[h] : 0.f;
+    const float sk = opt.no_sink ? -INFINITY : (sink ? sink[h] : 0.f);   // the row sees itself, so the maximum is finite
     const int g = h / (Hq / G);
     const int p = seq_past(pos, S) + t;
-    const int start = chunk > 0 ? (p / chunk) * chunk : 0;
+    const int start = first_key(p, chunk, opt.window);
     const int nkeys = p - start + 1;
     float* sq = sm;           // [D]
     float* sc = sm + D;       // [nkeys]
@@ -105,8 +174,6 @@ __global__ void __launch_bounds__(128) attn_chunk_sink_kernel(const float* __res
     }
     sum = block_sum(sum, red);   // contains the barrier that publishes sc[]
     const float inv = 1.f / (expf(sk - mx) + sum);
-    float gv = 1.f;
-    if (gate) gv = 1.f / (1.f + expf(-ldf(gate + (size_t)t * ld_gate + h)));
     for (int c = threadIdx.x; c < DV; c += blockDim.x) {
         float acc = 0.f;
         for (int jk = 0; jk < nkeys; ++jk) {
@@ -114,6 +181,7 @@ __global__ void __launch_bounds__(128) attn_chunk_sink_kernel(const float* __res
             const T* vr = v_pages + (((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size) * ld_v;
             acc = fmaf(sc[jk], ldf(vr + c), acc);
         }
+        const float gv = gate ? gate_of(gate, ld_gate, t, h, c, DV, opt.gate_channel) : 1.f;
         stf(out + (size_t)t * ld_out + (size_t)h * DV + c, acc * inv * gv);
     }
 }
@@ -151,7 +219,7 @@ __global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict
                                                          int page_size, const T* __restrict__ gate, int ld_gate,
                                                          T* __restrict__ out, int ld_out, int S, int Hq, int G, int D, int DV,
                                                          float scale, SeqPos pos, const float* __restrict__ sink, int ld_v,
-                                                         float* __restrict__ part, int* __restrict__ counters) {
+                                                         float* __restrict__ part, int* __restrict__ counters, AttnOpts opt) {
     if (seq_done(pos)) return;
     extern __shared__ float sm[];
     __shared__ float red[32];
@@ -163,6 +231,8 @@ __global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict
     const int t = blockIdx.y, h = blockIdx.x, z = blockIdx.z, nz = gridDim.z;
     const int g = h / (Hq / G);
     const int nkeys = seq_past(pos, S) + t + 1;
+    // with a window the walk starts at the tile that holds the row's first key; keys of that tile before it are masked
+    const int kfirst = first_key(nkeys - 1, 0, opt.window), tile0 = kfirst / kSplitKeys;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int i = threadIdx.x; i < D; i += blockDim.x) sq[i] = q[((size_t)t * Hq + h) * D + i] * scale;
     float m = -INFINITY, l = 0.f;
@@ -170,7 +240,7 @@ __global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict
     constexpr int VN = VEC ? RowVec<T>::N : 1, NP = VEC ? 128 * kSplitMaxOut / (32 * RowVec<T>::N) : 1;
     float ov[NP][VN] = {};                           // vector form: a warp's sum over ITS keys of 16-byte pieces lane, lane + 32, ...
     float* osum = sc + kSplitKeys;                   // [4][DV], vector form only
-    for (int k0 = z * kSplitKeys; k0 < nkeys; k0 += nz * kSplitKeys) {
+    for (int k0 = (tile0 + z) * kSplitKeys; k0 < nkeys; k0 += nz * kSplitKeys) {
         const int nk = min(kSplitKeys, nkeys - k0);
         __syncthreads();       // sq is staged; the previous tile's weights are consumed
         // every key's row in the page pool first (one page-table read per thread, all in flight together)
@@ -211,7 +281,8 @@ __global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict
             }
 #pragma unroll
             for (int j = 0; j < KG; ++j) {
-                const float v = warp_sum(acc[j]);
+                float v = warp_sum(acc[j]);
+                if (k0 + j0 + j < kfirst) v = -INFINITY;       // before the window (first tile only)
                 if (j0 + j < nk) {
                     if (lane == 0) sc[j0 + j] = v;
                     mx = fmaxf(mx, v);
@@ -305,19 +376,18 @@ __global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict
     if (!last_flag) return;
     __threadfence();
     const float* all = part + ((size_t)t * Hq + h) * nz * (DV + 2);
-    const float sk = sink ? sink[h] : 0.f;
+    const float sk = opt.no_sink ? -INFINITY : (sink ? sink[h] : 0.f);   // split 0 holds the row's first key: mt is finite
     float mt = sk;
     for (int i = 0; i < nz; ++i) mt = fmaxf(mt, __ldcg(all + (size_t)i * (DV + 2)));
     float lt = expf(sk - mt);                       // the sink: weight in the denominator, no value
     for (int i = 0; i < nz; ++i) lt = fmaf(__ldcg(all + (size_t)i * (DV + 2) + 1), expf(__ldcg(all + (size_t)i * (DV + 2)) - mt), lt);
-    float gv = 1.f;
-    if (gate) gv = 1.f / (1.f + expf(-ldf(gate + (size_t)t * ld_gate + h)));
-    const float f = gv / lt;
+    const float f = 1.f / lt;
     for (int c = threadIdx.x; c < DV; c += blockDim.x) {
         float acc = 0.f;
         for (int i = 0; i < nz; ++i)
             acc = fmaf(__ldcg(all + (size_t)i * (DV + 2) + 2 + c), expf(__ldcg(all + (size_t)i * (DV + 2)) - mt), acc);
-        stf(out + (size_t)t * ld_out + (size_t)h * DV + c, acc * f);
+        const float gv = gate ? gate_of(gate, ld_gate, t, h, c, DV, opt.gate_channel) : 1.f;
+        stf(out + (size_t)t * ld_out + (size_t)h * DV + c, acc * f * gv);
     }
     if (threadIdx.x == 0) counters[t * Hq + h] = 0;
 }
@@ -353,7 +423,7 @@ __global__ void __launch_bounds__(256) attn_chunk_sink_tiled_kernel(const float*
                                                                     int page_size, const T* __restrict__ gate, int ld_gate,
                                                                     T* __restrict__ out, int ld_out, int S, int Hq, int G, int D, int DV,
                                                                     int chunk, float scale, SeqPos pos,
-                                                                    const float* __restrict__ sink, int ld_v) {
+                                                                    const float* __restrict__ sink, int ld_v, AttnOpts opt) {
     if (seq_done(pos)) return;
     extern __shared__ __align__(16) uint8_t smem_attn[];
     const int dc = min(D, ADC);
@@ -368,17 +438,18 @@ __global__ void __launch_bounds__(256) attn_chunk_sink_tiled_kernel(const float*
     const int past = seq_past(pos, S);
     const int rows = min(AQ, S - t0);
     const int pf = past + t0, pl = pf + rows - 1;
-    const int kbeg = chunk > 0 ? (pf / chunk) * chunk : 0;
+    const int kbeg = first_key(pf, chunk, opt.window);       // the first row's first key: no later row starts earlier
     const int tm = (threadIdx.x / 16) * 4, tn = (threadIdx.x % 16) * 4;
     const int lr = threadIdx.x / 16, lc = threadIdx.x % 16;              // staging: 16 threads walk a row
     int p_row[4], lo_row[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         p_row[i] = pf + tm + i;
-        lo_row[i] = chunk > 0 ? (p_row[i] / chunk) * chunk : 0;
+        lo_row[i] = first_key(p_row[i], chunk, opt.window);
     }
-    const float sk = sink ? sink[blockIdx.x] : 0.f;
-    float m[4] = {sk, sk, sk, sk}, l[4] = {1.f, 1.f, 1.f, 1.f};
+    const float sk = opt.no_sink ? kNoSinkMax : (sink ? sink[blockIdx.x] : 0.f);
+    const float l0 = opt.no_sink ? 0.f : 1.f;
+    float m[4] = {sk, sk, sk, sk}, l[4] = {l0, l0, l0, l0};
     float o[4][8] = {};
     const float* qh = q + ((size_t)t0 * Hq + h) * D;
     const bool q_once = D <= ADC;
@@ -487,13 +558,14 @@ __global__ void __launch_bounds__(256) attn_chunk_sink_tiled_kernel(const float*
     for (int i = 0; i < 4; ++i) {
         const int t = t0 + tm + i;
         if (tm + i >= rows) continue;
-        float gv = 1.f;
-        if (gate) gv = 1.f / (1.f + expf(-ldf(gate + (size_t)t * ld_gate + h)));
-        const float f = gv / l[i];
+        const float f = 1.f / l[i];
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
             const int col = c0 + (c < 4 ? tn + c : 64 + tn + c - 4);
-            if (col < DV) stf(out + (size_t)t * ld_out + (size_t)h * DV + col, o[i][c] * f);
+            if (col < DV) {
+                const float gv = gate ? gate_of(gate, ld_gate, t, h, col, DV, opt.gate_channel) : 1.f;
+                stf(out + (size_t)t * ld_out + (size_t)h * DV + col, o[i][c] * f * gv);
+            }
         }
     }
 }
@@ -501,7 +573,7 @@ __global__ void __launch_bounds__(256) attn_chunk_sink_tiled_kernel(const float*
 template <typename T>
 int launch_attn_tiled(const float* q, const void* k_pages, const void* v_pages, const int* page_table, int page_size,
                       const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D, int DV, int chunk,
-                      float scale, SeqPos pos, cudaStream_t s, const float* sink, int ld_v) {
+                      float scale, SeqPos pos, cudaStream_t s, const float* sink, int ld_v, AttnOpts opt) {
     static SmemAttrOnce once;
     const size_t smem = attn_tiled_smem<T>(ADC);
     if (ensure_dyn_smem(once, attn_chunk_sink_tiled_kernel<T>, (int)smem)) return -100;
@@ -509,7 +581,7 @@ int launch_attn_tiled(const float* q, const void* k_pages, const void* v_pages, 
     count_launch();
     attn_chunk_sink_tiled_kernel<T><<<grid, 256, attn_tiled_smem<T>(D), s>>>(q, (const T*)k_pages, (const T*)v_pages, page_table, page_size,
                                                                             (const T*)gate, ld_gate, (T*)out, ld_out, S, Hq, G, D, DV,
-                                                                            chunk, scale, pos, sink, ld_v);
+                                                                            chunk, scale, pos, sink, ld_v, opt);
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }
 
@@ -538,7 +610,7 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
                                                                   int page_size, const bf16* __restrict__ gate, int ld_gate,
                                                                   bf16* __restrict__ out, int ld_out, int S, int Hq, int G, int D, int DV,
                                                                   int chunk, float scale, SeqPos pos,
-                                                                  const float* __restrict__ sink, int ld_v) {
+                                                                  const float* __restrict__ sink, int ld_v, AttnOpts opt) {
     if (seq_done(pos)) return;
     extern __shared__ __align__(16) uint8_t smem_attn[];
     // NV output tiles of 128 channels per CTA (NV = 2: values of up to 256 channels against one pass over the scores)
@@ -553,7 +625,7 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
     const int past = seq_past(pos, S);
     const int rows = min(MQ, S - t0);
     const int pf = past + t0, pl = pf + rows - 1;
-    const int kbeg = chunk > 0 ? (pf / chunk) * chunk : 0;
+    const int kbeg = first_key(pf, chunk, opt.window);       // the first row's first key: no later row starts earlier
     const int dvv = min(MVW, DV - c0), DVp = (dvv + 15) / 16 * 16;
     const int warp = (threadIdx.x >> 5) & 3, kh = threadIdx.x >> 7, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
     // queries: fp32 -> bf16, zero padding
@@ -568,12 +640,13 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         p_row[i] = pf + r_lo + 8 * i;
-        lo_row[i] = chunk > 0 ? (p_row[i] / chunk) * chunk : 0;
+        lo_row[i] = first_key(p_row[i], chunk, opt.window);
     }
-    const float sk = sink ? sink[blockIdx.x] : 0.f;
+    const float sk = opt.no_sink ? kNoSinkMax : (sink ? sink[blockIdx.x] : 0.f);
     float m[2] = {sk, sk};
     // per-thread partial sums; the sink's 1 is counted once per row (by one thread of the first group of warps)
-    float l[2] = {(tq == 0 && kh == 0) ? 1.f : 0.f, (tq == 0 && kh == 0) ? 1.f : 0.f};
+    const float l0 = (tq == 0 && kh == 0 && !opt.no_sink) ? 1.f : 0.f;
+    float l[2] = {l0, l0};
     float o[16 * NV][4] = {};
     // VEC8: a tile's K and V rows arrive by 16-byte asynchronous copies (zero-filled past the last key and in the padding
     // columns), all in flight together, into the buffer the previous tile does not use, while that tile is computed
@@ -644,7 +717,7 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
         // A tile every row of the CTA sees in full (at or after the last row's chunk start, wholly before the first row)
         // skips the mask. The exponentials are exp2 of pre-scaled arguments: their error (2^-22) is far below the bf16
         // rounding of the weights that follows.
-        const bool full = k0 + MK - 1 <= pf && rows == MQ && (chunk <= 0 || k0 >= (pl / chunk) * chunk);
+        const bool full = k0 + MK - 1 <= pf && rows == MQ && k0 >= first_key(pl, chunk, opt.window);
         float corr[2];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -739,22 +812,24 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
         lt += __shfl_xor_sync(0xffffffffu, lt, 2);
         const int r = r_lo + 8 * i, t = t0 + r;
         if (r >= rows) continue;
-        float gv = 1.f;
-        if (gate) gv = 1.f / (1.f + expf(-ldf(gate + (size_t)t * ld_gate + h)));
-        const float f = gv / lt;
+        const float gh = (gate && !opt.gate_channel) ? gate_of(gate, ld_gate, t, h, 0, DV, false) : 1.f;
+        const float f = gh / lt;
 #pragma unroll
         for (int nt = 0; nt < 16 * NV; ++nt)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int col = nt * 8 + 2 * tq + e;
-                if (col < dvv) stf(out + (size_t)t * ld_out + (size_t)h * DV + c0 + col, o[nt][2 * i + e] * f);
+                if (col < dvv) {
+                    const float gv = (gate && opt.gate_channel) ? gate_of(gate, ld_gate, t, h, c0 + col, DV, true) : 1.f;
+                    stf(out + (size_t)t * ld_out + (size_t)h * DV + c0 + col, o[nt][2 * i + e] * f * gv);
+                }
             }
     }
 }
 
 int launch_attn_mma(const float* q, const void* k_pages, const void* v_pages, const int* page_table, int page_size,
                     const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D, int DV, int chunk,
-                    float scale, SeqPos pos, cudaStream_t s, const float* sink, int ld_v) {
+                    float scale, SeqPos pos, cudaStream_t s, const float* sink, int ld_v, AttnOpts opt) {
     static SmemAttrOnce once82, once81, once1, once81w, once1w;
     const int Dp = (D + 15) / 16 * 16;
     // 16-byte copies need every K and V row (and the output-channel slice) to start on a 16-byte boundary
@@ -774,7 +849,7 @@ int launch_attn_mma(const float* q, const void* k_pages, const void* v_pages, co
         if (ensure_dyn_smem(ONCE, attn_chunk_sink_mma_kernel<VEC, KHN, NVN>, (int)smem_max)) return -100;                         \
         attn_chunk_sink_mma_kernel<VEC, KHN, NVN><<<grid, 128 * KHN, smem, s>>>(q, (const bf16*)k_pages, (const bf16*)v_pages, page_table, \
                                                                            page_size, (const bf16*)gate, ld_gate, (bf16*)out, ld_out, \
-                                                                           S, Hq, G, D, DV, chunk, scale, pos, sink, ld_v);  \
+                                                                           S, Hq, G, D, DV, chunk, scale, pos, sink, ld_v, opt);  \
     } while (0)
     if (two) LCC_ATTN_MMA(once82, true, 2, 1);
     else if (wide && vec8) LCC_ATTN_MMA(once81w, true, 1, 2);
@@ -811,14 +886,43 @@ int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_p
                     int page_size, const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D,
                     int DV, int chunk, float scale, bool tensor_cores, SeqPos pos, cudaStream_t s, const float* sink, int ld_v,
                     float* split_ws, size_t split_ws_floats, int key_hint) {
+    return attn_masked(dt, q, k_pages, v_pages, page_table, page_size, gate, ld_gate, out, ld_out, S, Hq, G, D, DV, chunk, scale,
+                       tensor_cores, pos, s, AttnOpts{0, false, false}, sink, ld_v, split_ws, split_ws_floats, key_hint);
+}
+
+int qk_headnorm_rope_append(int dt, const void* proj, int ld, int v_col, const float* qn_w, const float* kn_w, float eps,
+                            const float* inv_freq, float mag, int rot_dims, int rot_pairs, float* q_out, void* k_pages,
+                            void* v_pages, const int* page_table, int page_size, int S, int Hq, int G, int D, int DV, SeqPos pos,
+                            cudaStream_t s) {
+    if (!proj || !q_out || !k_pages || !v_pages || !page_table || S < 1 || Hq < 1 || G < 1 || D < 1 || DV < 1 || page_size < 1 ||
+        rot_dims < 0 || (rot_dims & 1) || rot_dims > D || (rot_dims > 0 && !inv_freq) || v_col < 0 || v_col + G * DV > ld)
+        return -2;
+    count_launch();
+    if (dt == DT_F32)
+        qk_headnorm_rope_append_kernel<float><<<S, 256, 0, s>>>((const float*)proj, ld, v_col, qn_w, kn_w, eps, inv_freq, mag, rot_dims,
+                                                                rot_pairs, q_out, (float*)k_pages, (float*)v_pages, page_table, page_size,
+                                                                S, Hq, G, D, DV, pos);
+    else
+        qk_headnorm_rope_append_kernel<bf16><<<S, 256, 0, s>>>((const bf16*)proj, ld, v_col, qn_w, kn_w, eps, inv_freq, mag, rot_dims,
+                                                               rot_pairs, q_out, (bf16*)k_pages, (bf16*)v_pages, page_table, page_size,
+                                                               S, Hq, G, D, DV, pos);
+    return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}
+
+int attn_masked(int dt, const float* q, const void* k_pages, const void* v_pages, const int* page_table, int page_size,
+                const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D, int DV, int chunk, float scale,
+                bool tensor_cores, SeqPos pos, cudaStream_t s, const AttnOpts& opt, const float* sink, int ld_v, float* split_ws,
+                size_t split_ws_floats, int key_hint) {
     if (!q || !k_pages || !v_pages || !page_table || !out || S < 1 || Hq < 1 || G < 1 || Hq % G || D < 1 || DV < 1)
         return -2;
     if (ld_v <= 0) ld_v = DV;
     if (ld_v < DV) return -2;
-    // few rows of plain causal attention over a long or device-known window: key splits across CTAs
-    const int keys_est = pos.kv_len ? std::max(key_hint, pos.past + S) : pos.past + S;
+    const int window = opt.window > 0 ? opt.window : 0;
+    // few rows without chunks over a long or device-known range of keys: key splits across CTAs
+    int keys_est = pos.kv_len ? std::max(key_hint, pos.past + S) : pos.past + S;
+    if (window) keys_est = std::min(keys_est, window + kSplitKeys);   // the window, plus the masked head of its first tile
     if (chunk <= 0 && S < kAttnTiledMin && split_ws && DV <= 128 * kSplitMaxOut && Hq <= kSplitMaxHeads &&
-        (pos.kv_len || keys_est > 2 * kSplitKeys)) {
+        ((pos.kv_len && !window) || keys_est > 2 * kSplitKeys)) {
         const size_t per = (size_t)S * Hq * (DV + 2), cnt = kSplitCounters;
         int nz = std::min(32, std::max(1, (keys_est + kSplitKeys - 1) / kSplitKeys));
         if (split_ws_floats > cnt) nz = (int)std::min<size_t>(nz, (split_ws_floats - cnt) / per);
@@ -830,7 +934,7 @@ int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_p
             count_launch();
 #define LCC_SPLIT(T, VECB)                                                                                                   \
     attn_split_kernel<T, VECB><<<grid, 128, smem, s>>>(q, (const T*)k_pages, (const T*)v_pages, page_table, page_size, (const T*)gate,  \
-                                                       ld_gate, (T*)out, ld_out, S, Hq, G, D, DV, scale, pos, sink, ld_v, part, counters)
+                                                       ld_gate, (T*)out, ld_out, S, Hq, G, D, DV, scale, pos, sink, ld_v, part, counters, opt)
             if (smem > 48 * 1024) return -3;
             if (dt == DT_F32) {
                 if (((D | DV | ld_v) % 4) == 0 && (((uintptr_t)k_pages | (uintptr_t)v_pages) % 16) == 0) LCC_SPLIT(float, true); else LCC_SPLIT(float, false);
@@ -841,22 +945,24 @@ int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_p
             return cudaGetLastError() == cudaSuccess ? 0 : -100;
         }
     }
-    // The one-CTA-per-row kernel keeps one score per key of the longest window a row of this call can have in shared memory.
-    // Windows that do not fit (or whose length only the device knows, in a replayed step without chunks) go to the tiled
-    // kernels, which walk the keys in tiles and take any row count.
+    // The one-CTA-per-row kernel keeps one score per key of the longest range a row of this call can see in shared memory
+    // (a chunk, a window, or everything cached when the host knows the length). Ranges that do not fit (or whose length only
+    // the device knows, in a replayed step without chunks or window) go to the tiled kernels, which walk the keys in tiles
+    // and take any row count.
     int max_keys = chunk > 0 ? chunk : -1;
-    if (!pos.kv_len) max_keys = chunk > 0 ? std::min(chunk, pos.past + S) : pos.past + S;
+    if (window) max_keys = max_keys > 0 ? std::min(max_keys, window) : window;
+    if (!pos.kv_len) max_keys = max_keys > 0 ? std::min(max_keys, pos.past + S) : pos.past + S;
     const size_t smem = sizeof(float) * ((size_t)D + (size_t)std::max(max_keys, 0));
     static const bool force_tiled = [] { const char* e = getenv("LIVECC_B200_SEQ_ATTN_TILED"); return e && e[0] == '1'; }();
     if (S >= kAttnTiledMin || max_keys < 0 || smem > 160 * 1024 || force_tiled) {
         if (dt == DT_BF16 && tensor_cores && D <= kAttnMmaMaxDim)
             return launch_attn_mma(q, k_pages, v_pages, page_table, page_size, gate, ld_gate, out, ld_out, S, Hq, G, D, DV, chunk,
-                                   scale, pos, s, sink, ld_v);
+                                   scale, pos, s, sink, ld_v, opt);
         if (dt == DT_F32)
             return launch_attn_tiled<float>(q, k_pages, v_pages, page_table, page_size, gate, ld_gate, out, ld_out, S, Hq, G, D, DV,
-                                            chunk, scale, pos, s, sink, ld_v);
+                                            chunk, scale, pos, s, sink, ld_v, opt);
         return launch_attn_tiled<bf16>(q, k_pages, v_pages, page_table, page_size, gate, ld_gate, out, ld_out, S, Hq, G, D, DV, chunk,
-                                       scale, pos, s, sink, ld_v);
+                                       scale, pos, s, sink, ld_v, opt);
     }
     dim3 grid(S, Hq);
     count_launch();
@@ -864,12 +970,12 @@ int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_p
         if (smem > 48 * 1024) cudaFuncSetAttribute(attn_chunk_sink_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attn_chunk_sink_kernel<float><<<grid, 128, smem, s>>>(q, (const float*)k_pages, (const float*)v_pages, page_table,
                                                               page_size, (const float*)gate, ld_gate, (float*)out, ld_out, S, Hq,
-                                                              G, D, DV, chunk, scale, pos, sink, ld_v);
+                                                              G, D, DV, chunk, scale, pos, sink, ld_v, opt);
     } else {
         if (smem > 48 * 1024) cudaFuncSetAttribute(attn_chunk_sink_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attn_chunk_sink_kernel<bf16><<<grid, 128, smem, s>>>(q, (const bf16*)k_pages, (const bf16*)v_pages, page_table,
                                                              page_size, (const bf16*)gate, ld_gate, (bf16*)out, ld_out, S, Hq, G,
-                                                             D, DV, chunk, scale, pos, sink, ld_v);
+                                                             D, DV, chunk, scale, pos, sink, ld_v, opt);
     }
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }

@@ -17,6 +17,7 @@ enum GemmEpilogue {
     EPI_SWIGLU = 6,          // C[:, j] = bf16(silu(bf16 gate_j) * bf16 up_j), gate/up rows interleaved by 16
     EPI_PARTIAL_F32 = 7,     // internal (split-K): fp32 partial tiles, reduced by splitk_reduce_kernel
     EPI_RELU2 = 8,           // C = bf16(relu(acc)^2)
+    EPI_GELU_TANH = 9,       // C = bf16(gelu_tanh(acc)), the activation in fp32 on the accumulator
 };
 
 struct GemmArgs {

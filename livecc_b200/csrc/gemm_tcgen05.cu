@@ -122,6 +122,10 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&v)[32], bf16* C,
 #pragma unroll
                     for (int j = 0; j < 8; ++j) { x[j] = fmaxf(x[j], 0.f); x[j] *= x[j]; }
                 }
+                if (EPI == EPI_GELU_TANH) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) x[j] = 0.5f * x[j] * (1.f + tanhf(0.7978845608028654f * (x[j] + 0.044715f * x[j] * x[j] * x[j])));
+                }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) x[j] = rbf(x[j]);
                 if (EPI == EPI_BIAS_QUICKGELU) {
@@ -601,6 +605,7 @@ static int launch_epi(const GemmArgs& a, int bn, int num_sms, cudaStream_t strea
         case EPI_BIAS_RESIDUAL: return launch_cfg<EPI_BIAS_RESIDUAL>(a, bn, num_sms, stream);
         case EPI_SWIGLU: return launch_cfg<EPI_SWIGLU>(a, bn, num_sms, stream);
         case EPI_RELU2: return launch_cfg<EPI_RELU2>(a, bn, num_sms, stream);
+        case EPI_GELU_TANH: return launch_cfg<EPI_GELU_TANH>(a, bn, num_sms, stream);
     }
     return -14;
 }
@@ -736,7 +741,7 @@ int gemm_bf16_tn(const GemmArgs& a, int num_sms, cudaStream_t stream) {
         block_n = forced > 0 ? forced : choose_bn(a.M, a.N, num_sms);
     }
     // block_n < 0 selects the CTA-pair kernel with tile width -block_n (explicit: tests and tuning)
-    const bool pair = block_n < 0 && plain && a.epi != EPI_RELU2;
+    const bool pair = block_n < 0 && plain && a.epi != EPI_RELU2 && a.epi != EPI_GELU_TANH;
     if (block_n < 0) block_n = -block_n;
     if (block_n < 32 || block_n > 256 || (block_n % 16) || (a.epi == EPI_SWIGLU && (block_n % 32))) return -6;
     if (pair) return (block_n % 32) ? -6 : launch_epi2(a, block_n, num_sms, stream);

@@ -29,6 +29,7 @@ struct Grp {
 };
 __device__ __forceinline__ float act_of(float v, int act) {
     if (act == ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
+    else if (act == ACT_GELU_TANH) v = 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
     return v;
 }
 

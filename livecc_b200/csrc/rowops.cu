@@ -208,9 +208,82 @@ __global__ void __launch_bounds__(256) gather_rmsnorm_kernel(const float* __rest
     for (int c = threadIdx.x; c < W; c += blockDim.x) stf(out + (size_t)i * W + c, x[c] * rn * w[c]);
 }
 
-__global__ void softcap_kernel(float* __restrict__ x, int64_t n, float cap, float inv_cap) {
+__global__ void softcap_kernel(float* __restrict__ x, int64_t n, float cap, float inv_cap, float scale) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) x[i] = cap * tanhf(x[i] * inv_cap);
+    if (i < n) x[i] = (cap > 0.f ? cap * tanhf(x[i] * inv_cap) : x[i]) * scale;
+}
+
+__device__ __forceinline__ float norm_apply(const NormSpec& n, float v, float rn, int c) {
+    return n.kind == NORM_DYT ? fmaf(tanhf(n.alpha * v), n.w[c], n.b[c]) : v * rn * n.w[c];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) gather_norm_kernel(const float* __restrict__ x32, const int* __restrict__ rows, NormSpec n,
+                                                          T* __restrict__ out, int W) {
+    __shared__ float red[32];
+    const int i = blockIdx.x;
+    const float* x = x32 + (size_t)rows[i] * W;
+    float rn = 1.f;
+    if (n.kind == NORM_RMS) {
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < W; c += blockDim.x) ss = fmaf(x[c], x[c], ss);
+        ss = block_sum(ss, red);
+        rn = 1.f / sqrtf(ss / (float)W + n.eps);
+    }
+    for (int c = threadIdx.x; c < W; c += blockDim.x) stf(out + (size_t)i * W + c, norm_apply(n, x[c], rn, c));
+}
+
+// One CTA per row: pass 1 forms the new residual row (every addend read, also a row of xa that pass 2 rewrites) and, for a
+// norm with a row statistic, its sum of squares; pass 2 writes the normed row. A row's sums do not depend on S.
+template <typename T>
+__global__ void __launch_bounds__(256) residual_norm_kernel(float* __restrict__ x32, const T* __restrict__ a, int ld_a,
+                                                            const T* __restrict__ b, int ld_b, bool has_mc, MoeCombine mc, NormSpec n,
+                                                            T* __restrict__ xa, int W) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    float* x = x32 + (size_t)r * W;
+    float ss = 0.f;
+    if (a || b || has_mc) {
+        const float gs = (has_mc && mc.so) ? mc.gate[r] : 0.f;
+        for (int c = threadIdx.x; c < W; c += blockDim.x) {
+            float y = a ? ldf(a + (size_t)r * ld_a + c) : 0.f;
+            if (has_mc) {
+                float acc = 0.f;
+                for (int k = 0; k < mc.top; ++k) {
+                    const int p = mc.pos[(size_t)r * mc.top + k];
+                    if (p >= 0) acc = fmaf(mc.weight[(size_t)r * mc.top + k], ldf((const T*)mc.eo + (size_t)p * mc.ld_eo + c), acc);
+                }
+                if (mc.so) acc = fmaf(gs, ldf((const T*)mc.so + (size_t)r * mc.ld_so + c), acc);
+                y += acc;
+            } else if (b) {
+                y += ldf(b + (size_t)r * ld_b + c);
+            }
+            const float v = x[c] + y;
+            x[c] = v;
+            ss = fmaf(v, v, ss);
+        }
+    } else if (n.w && n.kind == NORM_RMS) {
+        for (int c = threadIdx.x; c < W; c += blockDim.x) ss = fmaf(x[c], x[c], ss);
+    }
+    if (!n.w) return;
+    float rn = 1.f;
+    if (n.kind == NORM_RMS) {
+        ss = block_sum(ss, red);
+        rn = 1.f / sqrtf(ss / (float)W + n.eps);
+    } else {
+        __syncthreads();       // every read of the old xa row (identity experts) is done before it is rewritten
+    }
+    for (int c = threadIdx.x; c < W; c += blockDim.x) stf(xa + (size_t)r * W + c, norm_apply(n, x[c], rn, c));
+}
+
+template <typename T>
+__global__ void glu_clamp_swish_kernel(const T* __restrict__ gu, int ld, T* __restrict__ out, int ld_out, int S, int F, float limit) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t)S * F) return;
+    const int r = (int)(i / F), c = (int)(i % F);
+    const float g = fminf(ldf(gu + (size_t)r * ld + c), limit);
+    const float u = fminf(fmaxf(ldf(gu + (size_t)r * ld + F + c), -limit), limit);
+    stf(out + (size_t)r * ld_out + c, g / (1.f + expf(-1.702f * g)) * (u + 1.f));
 }
 
 inline int done() { return cudaGetLastError() == cudaSuccess ? 0 : -100; }
@@ -301,11 +374,49 @@ int gather_rmsnorm(int dt, const float* x32, const int* rows, const float* w, fl
     return done();
 }
 
-int softcap(float* x, int64_t n, float cap, cudaStream_t s) {
+int softcap(float* x, int64_t n, float cap, cudaStream_t s, float scale) {
     if (!x || n < 1) return -2;
-    if (!(cap > 0.f)) return 0;
+    if (!(cap > 0.f) && scale == 1.f) return 0;
     count_launch();
-    softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(x, n, cap, 1.f / cap);
+    softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(x, n, cap > 0.f ? cap : 0.f, cap > 0.f ? 1.f / cap : 0.f, scale);
+    return done();
+}
+
+int gather_norm(int dt, const float* x32, const int* rows, const NormSpec& n, void* out, int n_rows, int W, cudaStream_t s) {
+    if (!x32 || !rows || !n.w || !out || n_rows < 1 || W < 1 || (n.kind == NORM_DYT && !n.b) || (n.kind != NORM_DYT && n.kind != NORM_RMS))
+        return -2;
+    count_launch();
+    if (dt == DT_F32)
+        gather_norm_kernel<float><<<n_rows, 256, 0, s>>>(x32, rows, n, (float*)out, W);
+    else
+        gather_norm_kernel<bf16><<<n_rows, 256, 0, s>>>(x32, rows, n, (bf16*)out, W);
+    return done();
+}
+
+int residual_norm(int dt, float* x32, const void* a, int ld_a, const void* b, int ld_b, const MoeCombine* mc, const NormSpec& next,
+                  void* xa, int S, int W, cudaStream_t s) {
+    if (!x32 || S < 1 || W < 1 || (next.w && !xa) || (next.w && next.kind == NORM_DYT && !next.b) ||
+        (next.kind != NORM_DYT && next.kind != NORM_RMS) || (mc && b))
+        return -2;
+    if (mc && (!mc->eo || !mc->pos || !mc->weight || mc->top < 1 || (mc->so && !mc->gate))) return -2;
+    if (!a && !b && !mc && !next.w) return 0;
+    count_launch();
+    const MoeCombine m = mc ? *mc : MoeCombine{};
+    if (dt == DT_F32)
+        residual_norm_kernel<float><<<S, 256, 0, s>>>(x32, (const float*)a, ld_a, (const float*)b, ld_b, mc != nullptr, m, next, (float*)xa, W);
+    else
+        residual_norm_kernel<bf16><<<S, 256, 0, s>>>(x32, (const bf16*)a, ld_a, (const bf16*)b, ld_b, mc != nullptr, m, next, (bf16*)xa, W);
+    return done();
+}
+
+int glu_clamp_swish(int dt, const void* gu, int ld, void* out, int ld_out, int S, int F, float limit, cudaStream_t s) {
+    if (!gu || !out || S < 1 || F < 1) return -2;
+    const int64_t n = (int64_t)S * F;
+    count_launch();
+    if (dt == DT_F32)
+        glu_clamp_swish_kernel<float><<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const float*)gu, ld, (float*)out, ld_out, S, F, limit);
+    else
+        glu_clamp_swish_kernel<bf16><<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const bf16*)gu, ld, (bf16*)out, ld_out, S, F, limit);
     return done();
 }
 

@@ -2,7 +2,8 @@
 // decode token per sequence) over every layer and produces the logits of the wanted rows. Prefill and decode use the
 // same launch sequence; what differs is the row count and which kernel of an op the shape selects.
 // A layer is a mixer (its output lands in one buffer), a feed-forward (dense or routed) and the block form around them
-// (post-norm residual, or pre-norm sublayers on several residual streams); the three are chosen independently per model.
+// (post-norm residual, pre-norm sublayers on several residual streams, or a parallel block whose mixer and feed-forward read
+// one normed row); the three are chosen independently per model.
 // The host (Python) owns every buffer; this file only sequences kernel launches.
 #include <stdlib.h>
 #include <string.h>
@@ -41,6 +42,8 @@ struct Dims {
     int t_nk, t_nv, t_proj, t_pack;      // retention: q and k columns, v columns, projection rows, fp32 pack [q | k | v]
     int a_nq, a_kv, a_kd, a_proj, a_gate, a_lat, a_o;   // latent attention: query columns, latent + key part, cache row, projection rows,
                                                         // gate column, absorbed-output columns, value columns
+    int m_nq, m_nk, m_nv, m_vcol, m_gate, m_ngate, m_proj, m_o;   // masked attention: q, k, projected v columns, the values' first column,
+                                                                  // the gate's first column and width, projection rows, output columns
 };
 Dims dims_of(const lcc_seq_layer& L) {
     Dims z{};
@@ -66,6 +69,14 @@ Dims dims_of(const lcc_seq_layer& L) {
         z.a_proj = z.a_gate + L.a_heads;
         z.a_lat = L.a_heads * L.a_rank;
         z.a_o = L.a_heads * L.a_vdim;
+    } else if (L.type == LCC_MIX_ATTENTION) {
+        z.m_nq = L.m_heads * L.m_dim; z.m_nk = L.m_kv_heads * L.m_dim;
+        z.m_nv = L.m_value_keys ? 0 : L.m_kv_heads * L.m_vdim;
+        z.m_vcol = L.m_value_keys ? z.m_nq : z.m_nq + z.m_nk;       // the values are the key columns as projected, or their own
+        z.m_gate = z.m_nq + z.m_nk + z.m_nv;
+        z.m_ngate = L.m_gate == LCC_GATE_CHANNEL ? L.m_heads * L.m_vdim : (L.m_gate == LCC_GATE_HEAD ? L.m_heads : 0);
+        z.m_proj = z.m_gate + z.m_ngate;
+        z.m_o = L.m_heads * L.m_vdim;
     }
     return z;
 }
@@ -79,7 +90,7 @@ constexpr int kMoeTcMinRows = 256;   // routed rows (tokens x top) from which th
 constexpr int kForkMaxRows = 32;     // rows up to which the shared expert runs on the second stream
 
 struct WsLayout {
-    size_t x32, xa, proj, proj2, mid, mid2, y32, q32, f1, f2, o1, o2, xf, scan, scan_floats, xsum, moe_f, moe_i, moe_x, moe_h, moe_o, split, split_floats, total;
+    size_t x32, xa, proj, proj2, mid, mid2, y32, q32, f1, f2, o1, o2, xf, scan, scan_floats, xsum, moe_f, moe_i, moe_x, moe_h, moe_g, moe_o, split, split_floats, total;
     int moe_rows;         // rows of the expert-sorted buffers: top per token, every list padded to a whole 128-row tile
     int w_proj, w_proj2, w_mid, w_y, w_q, w_f;
     int moe_e, moe_top;   // largest expert count and top-k of any layer (0: no routed feed-forward)
@@ -91,7 +102,7 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
     const size_t nt = NT > 0 ? NT : 1, nw = NW > 0 ? NW : 1;
     int wp = 8, wp2 = 8, wm = 8, wy = 8, wq = 8, wf = 8;
     size_t scan_floats = 0;
-    int moe_e = 0, moe_top = 0, moe_ff = 0, moe_rows = 0;
+    int moe_e = 0, moe_top = 0, moe_ff = 0, moe_rows = 0, moe_glu = 0;   // moe_glu: widest hidden row of a gated expert
     size_t split_floats = 0;   // key-split partials of few-row plain causal attention
     for (const lcc_seq_layer& l : m->layers) {
         const Dims z = dims_of(l);
@@ -115,11 +126,21 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
         }
         if (l.type == LCC_MIX_PARALLEL && l.l_chunk <= 0)
             split_floats = std::max(split_floats, lcc::attn_split_ws_floats(lcc::kAttnTiledMin - 1, l.l_heads, l.l_vdim));
+        if (l.type == LCC_MIX_ATTENTION) {
+            wp = std::max(wp, ld8(z.m_proj)); wm = std::max(wm, ld8(z.m_o)); wq = std::max(wq, z.m_nq);
+            if (l.m_chunk <= 0)
+                split_floats = std::max(split_floats, lcc::attn_split_ws_floats(lcc::kAttnTiledMin - 1, l.m_heads, l.m_vdim));
+        }
         if (l.ff_kind == LCC_FF_MOE) {
+            const bool glu = l.e_act == LCC_EXPERT_CLAMP_GLU;
             wm = std::max(wm, ld8(l.e_shared_ff));            // the shared expert's hidden row
-            moe_e = std::max(moe_e, l.e_experts); moe_top = std::max(moe_top, l.e_top); moe_ff = std::max(moe_ff, ld8(l.e_ff));
+            // logits row: every router output (real + identity experts), then the shared expert's gate
+            moe_e = std::max(moe_e, l.e_experts + l.e_identity); moe_top = std::max(moe_top, l.e_top);
+            moe_ff = std::max(moe_ff, ld8(glu ? 2 * l.e_ff : l.e_ff));
+            if (glu) moe_glu = std::max(moe_glu, ld8(l.e_ff));
             moe_rows = std::max(moe_rows, (int)nt * l.e_top + (l.e_experts + 1) * kMoeTile);
-        } else if (l.ff > 0) { wp = std::max(wp, ld8(2 * l.ff)); wm = std::max(wm, ld8(l.ff)); }
+        } else if (l.ff_kind == LCC_FF_MLP && l.ff > 0) { wm = std::max(wm, ld8(l.ff)); }
+        else if (l.ff > 0) { wp = std::max(wp, ld8(2 * l.ff)); wm = std::max(wm, ld8(l.ff)); }
     }
     L.moe_e = moe_e; L.moe_top = moe_top; L.moe_rows = moe_rows;
     L.w_proj = wp; L.w_proj2 = wp2; L.w_mid = wm; L.w_y = wy; L.w_q = wq; L.w_f = wf;
@@ -135,6 +156,7 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
     // expert-sorted rows: the gathered inputs (tensor-core route only), the hidden rows, the expert outputs
     L.moe_x = take(moe_e && m->use_tc && m->d.dtype == LCC_DT_BF16 ? (size_t)moe_rows * ld8(W) * es : 0);
     L.moe_h = take((size_t)moe_rows * moe_ff * es);
+    L.moe_g = take((size_t)moe_rows * moe_glu * es);
     L.moe_o = take((size_t)moe_rows * (moe_e ? ld8(W) : 0) * es);
     L.xa = take(nt * ld8(W) * es);
     L.proj = take(nt * wp * es);
@@ -175,7 +197,7 @@ int linear(const lcc_seq_model* m, const void* x, int ldx, const void* W, const 
         a.c_f32 = y_f32;
         a.A = x; a.B = W; a.C = y; a.M = M; a.N = Np; a.K = K; a.lda = ldx; a.ldb = K; a.ldc = ldy;
         a.bias = bias ? bias_st : nullptr; a.residual = nullptr; a.ldr = 0; a.block_n = 0;
-        a.epi = act == lcc::ACT_RELU2 ? lcc::EPI_RELU2 : (bias ? lcc::EPI_BIAS : lcc::EPI_NONE);
+        a.epi = act == lcc::ACT_RELU2 ? lcc::EPI_RELU2 : (act == lcc::ACT_GELU_TANH ? lcc::EPI_GELU_TANH : (bias ? lcc::EPI_BIAS : lcc::EPI_NONE));
         return lcc::gemm_bf16_tn(a, m->ctx->num_sms, s);
     }
     if (act != lcc::ACT_NONE) {   // the activation rides in the store of the CUDA-core kernels too
@@ -217,20 +239,33 @@ lcc_seq_model* lcc_seq_model_create(lcc_ctx* ctx, const lcc_seq_model_desc* desc
     if (desc->width < 1 || desc->vocab < 1 || desc->n_layers < 1) return fail("bad sizes");
     if (desc->dtype != LCC_DT_BF16 && desc->dtype != LCC_DT_F32) return fail("unknown storage type");
     if (!desc->embed || !desc->final_norm_f32 || !desc->head) return fail("missing weights");
-    const bool hc = desc->block == LCC_BLOCK_PRENORM_HC;
-    if (desc->block != LCC_BLOCK_POSTNORM && !hc) return fail("unknown block form");
+    const bool hc = desc->block == LCC_BLOCK_PRENORM_HC, par = desc->block == LCC_BLOCK_PARALLEL;
+    const bool dyt = desc->norm_kind == LCC_NORM_DYT;
+    if (desc->block != LCC_BLOCK_POSTNORM && !hc && !par) return fail("unknown block form");
+    if (desc->norm_kind != LCC_NORM_RMS && !dyt) return fail("unknown norm kind");
+    if (dyt && (!par || !desc->final_norm_bias_f32)) return fail("the Dynamic-Tanh norm is served in parallel blocks and needs its bias");
     if (hc && (desc->streams < 1 || desc->streams > 8)) return fail("1 to 8 residual streams");
     for (int i = 0; i < desc->n_layers; ++i) {
         const lcc_seq_layer& l = desc->layers[i];
         if (l.ff_kind == LCC_FF_MOE) {
             if (l.e_experts < 1 || l.e_experts > 512 || l.e_top < 1 || l.e_top > l.e_experts || l.e_ff < 1 || l.e_shared_ff < 0)
                 return fail("routed feed-forward: unsupported sizes");
-            if (!l.norm2_f32 || !l.e_router || !l.e_correction_f32 || !l.e_up || !l.e_down || (l.e_shared_ff > 0 && (!l.e_shared_up || !l.e_shared_down)))
+            if ((!par && !l.norm2_f32) || !l.e_router || !l.e_correction_f32 || !l.e_up || !l.e_down || (l.e_shared_ff > 0 && (!l.e_shared_up || !l.e_shared_down)))
                 return fail("routed feed-forward: missing weights");
-        } else if (l.ff_kind != LCC_FF_GLU) {
+            const int outs = l.e_experts + l.e_identity;
+            if (l.e_identity < 0 || outs > 512 || l.e_top > outs || (l.e_identity > 0 && (l.e_shared_ff > 0 || !par)))
+                return fail("routed feed-forward: identity experts are served in parallel blocks, without a shared expert");
+            if (l.e_groups < 0 || (l.e_groups > 0 && (outs % l.e_groups || l.e_keep < 1 || l.e_keep > l.e_groups || l.e_keep * (outs / l.e_groups) < l.e_top)))
+                return fail("routed feed-forward: the kept groups must be equal groups that hold at least `top` experts");
+            if (l.e_router_kind != LCC_ROUTER_SIGMOID && l.e_router_kind != LCC_ROUTER_SOFTMAX) return fail("unknown router kind");
+            if (l.e_act != LCC_EXPERT_RELU2 && l.e_act != LCC_EXPERT_CLAMP_GLU) return fail("unknown expert activation");
+        } else if (l.ff_kind != LCC_FF_GLU && l.ff_kind != LCC_FF_MLP) {
             return fail("unknown feed-forward kind");
         }
-        if (!l.norm1_f32 || (l.ff > 0 && (!l.norm2_f32 || !l.ff_in || !l.ff_out))) return fail("missing norm / feed-forward weights");
+        if (!l.norm1_f32 || (l.ff > 0 && ((!par && !l.norm2_f32) || !l.ff_in || !l.ff_out))) return fail("missing norm / feed-forward weights");
+        if (dyt && !l.norm1_bias_f32) return fail("missing norm bias");
+        if (par && l.type != LCC_MIX_ATTENTION) return fail("a parallel block takes the attention mixer");
+        if (!par && l.type == LCC_MIX_ATTENTION) return fail("the attention mixer is served in parallel blocks");
         if (hc && (!l.hc1_f32 || ((l.ff > 0 || l.ff_kind == LCC_FF_MOE) && !l.hc2_f32))) return fail("missing stream weights");
         if (hc && l.type == LCC_MIX_PARALLEL) return fail("the parallel mixer merges its branches in a post-norm block");
         if (l.type == LCC_MIX_SSD) {
@@ -264,6 +299,13 @@ lcc_seq_model* lcc_seq_model_create(lcc_ctx* ctx, const lcc_seq_model_desc* desc
             }
             if (!l.a_in || !l.a_uk_t || !l.a_uv || !l.a_sink_f32 || !l.a_out || !l.rot_inv_freq_f32)
                 return fail("latent attention layer: missing weights");
+        } else if (l.type == LCC_MIX_ATTENTION) {
+            if (l.m_heads < 1 || l.m_kv_heads < 1 || l.m_heads % l.m_kv_heads || l.m_dim < 1 || l.m_vdim < 1 || l.m_rot_dims < 0 ||
+                (l.m_rot_dims & 1) || l.m_rot_dims > l.m_dim || (l.m_value_keys && l.m_vdim != l.m_dim) || l.m_gate < LCC_GATE_NONE ||
+                l.m_gate > LCC_GATE_CHANNEL)
+                return fail("attention layer: unsupported sizes");
+            if (!l.m_in || !l.m_qnorm_f32 || !l.m_knorm_f32 || !l.m_out || (l.m_rot_dims > 0 && !l.rot_inv_freq_f32))
+                return fail("attention layer: missing weights");
         } else {
             return fail("unknown mixer type");
         }
@@ -315,7 +357,7 @@ int64_t lcc_seq_layer_state_floats(const lcc_seq_model* m, int layer) {
     const Dims z = dims_of(l);
     if (l.type == LCC_MIX_SSD) return (int64_t)z.conv_ch * (l.s_conv - 1) + (int64_t)l.s_heads * l.s_vdim * l.s_state;
     if (l.type == LCC_MIX_RETENTION) return (int64_t)l.t_heads * l.t_vdim * l.t_dim;
-    if (l.type == LCC_MIX_LATENT) return 0;
+    if (l.type == LCC_MIX_LATENT || l.type == LCC_MIX_ATTENTION) return 0;
     return (int64_t)l.r_heads * l.r_vdim * l.r_dim;
 }
 
@@ -344,8 +386,14 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
     uint8_t* o1 = ws + L.o1; uint8_t* o2 = ws + L.o2; uint8_t* xf = ws + L.xf;
     float* scan_ws = L.scan_floats ? (float*)(ws + L.scan) : nullptr;
     float* split_ws = L.split_floats ? (float*)(ws + L.split) : nullptr;
-    const bool hc = d.block == LCC_BLOCK_PRENORM_HC;
+    const bool hc = d.block == LCC_BLOCK_PRENORM_HC, par = d.block == LCC_BLOCK_PARALLEL;
     const int NS = hc ? d.streams : 1;
+    // parallel blocks: the norm that opens layer i (none past the last layer)
+    auto norm_of = [&](int i) {
+        if (i >= d.n_layers) return lcc::NormSpec{d.norm_kind, nullptr, nullptr, 0.f, d.eps};
+        const lcc_seq_layer& n = m->layers[i];
+        return lcc::NormSpec{d.norm_kind, n.norm1_f32, n.norm1_bias_f32, n.norm1_alpha, d.eps};
+    };
     float* xsum = (float*)(ws + L.xsum);
     // pre-norm blocks: the sublayer output that the next boundary kernel folds into the streams
     const float* pend_hc = nullptr;
@@ -375,6 +423,7 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
                                      pos_of(en), s, NS), "embedding");
             r0 += en.n_new;
         }
+        if (par) STEP(lcc::residual_norm(dt, x32, nullptr, 0, nullptr, 0, nullptr, norm_of(0), xa, T, W, s), "first norm");
     }
     for (int li = 0; li < d.n_layers; ++li) {
         const lcc_seq_layer& l = m->layers[li];
@@ -444,6 +493,30 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
             }
             STEP(linear_heads(m, mid, ldl, l.a_rank, l.a_uv, mid2, ldo, l.a_vdim, false, H, T, l.a_vdim, l.a_rank, s), "value up-projection");
             STEP(linear(m, mid2, ldo, l.a_out, nullptr, o1, W, false, T, W, z.a_o, s), "latent attention out-proj");
+        } else if (l.type == LCC_MIX_ATTENTION) {
+            // [q | k | (v) | gate] -> per-head q/k norm + rotary positions, k and the values (the key columns as projected, or
+            // their own) into the pages -> attention inside the window -> sigmoid gate (in the attention kernel's store) -> out-proj
+            const int ldp = ld8(z.m_proj), ldo = ld8(z.m_o);
+            STEP(linear(m, xa, W, l.m_in, nullptr, proj, ldp, false, T, z.m_proj, W, s), "attention in-proj");
+            const lcc::AttnOpts ao{l.m_window, !l.m_sink, l.m_gate == LCC_GATE_CHANNEL};
+            int r0 = 0;
+            for (int e = 0; e < n_entries; ++e) {
+                const lcc_seq_entry& en = entries[e];
+                if (!en.k_pages || !en.v_pages || !en.k_pages[li] || !en.v_pages[li] || !en.page_table)
+                    LCC_FAIL(m->ctx, -2, "lcc_seq_forward: entry %d has no pages for layer %d", e, li);
+                const lcc::SeqPos pos = pos_of(en);
+                uint8_t* pr = proj + (size_t)r0 * ldp * es;
+                float* q = q32 + (size_t)r0 * z.m_nq;
+                STEP(lcc::qk_headnorm_rope_append(dt, pr, ldp, z.m_vcol, l.m_qnorm_f32, l.m_knorm_f32, d.eps, l.rot_inv_freq_f32, l.rot_mag,
+                                                  l.m_rot_dims, l.m_rot_pairs, q, en.k_pages[li], en.v_pages[li], en.page_table, page_size,
+                                                  en.n_new, l.m_heads, l.m_kv_heads, l.m_dim, l.m_vdim, pos, s), "q/k norm + rotary + cache append");
+                STEP(lcc::attn_masked(dt, q, en.k_pages[li], en.v_pages[li], en.page_table, page_size,
+                                      z.m_ngate ? pr + (size_t)z.m_gate * es : nullptr, ldp, mid + (size_t)r0 * ldo * es, ldo, en.n_new,
+                                      l.m_heads, l.m_kv_heads, l.m_dim, l.m_vdim, l.m_chunk, l.m_scale, m->use_tc, pos, s, ao, nullptr, 0,
+                                      split_ws, L.split_floats, en.past + en.n_new), "window attention");
+                r0 += en.n_new;
+            }
+            STEP(linear(m, mid, ldo, l.m_out, nullptr, o1, W, false, T, W, z.m_o, s), "attention out-proj");
         } else if (l.type == LCC_MIX_SSD) {
             const int ldp = ld8(z.s_proj), ldm = ld8(z.conv_ch), GN = l.s_groups * l.s_state;
             STEP(linear(m, xa, W, l.s_in, nullptr, proj, ldp, false, T, z.s_proj, W, s), "state-space in-proj");
@@ -533,19 +606,28 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
         }
         // ---- the mixer's output is in o1 ----
         if (hc) pend_hc = l.hc1_f32;
+        else if (par) {}   // the feed-forward reads the same normed row; the residual sum closes the layer
         else if (l.type != LCC_MIX_PARALLEL)
             STEP(lcc::postnorm_residual(dt, x32, xa, o1, W, nullptr, nullptr, 0, nullptr, l.norm1_f32, d.alpha, d.eps, T, W, s), "norm1");
         const bool has_ff = l.ff > 0 || l.ff_kind == LCC_FF_MOE;
         if (has_ff && hc) STEP(boundary(l.hc2_f32, l.norm2_f32, nullptr), "stream boundary");
+        lcc::MoeCombine par_mc{};       // parallel block: the routed feed-forward's row is formed by the layer's residual kernel
+        bool par_is_mc = false;
         if (l.ff_kind == LCC_FF_MOE) {
-            const int E = l.e_experts, K = l.e_top, lde = ld8(E + 1), ldh = ld8(l.e_ff), ldw8 = ld8(W), lds = ld8(l.e_shared_ff);
+            // E real experts own row lists; the router has EO = E + identity outputs
+            const bool glu = l.e_act == LCC_EXPERT_CLAMP_GLU;
+            const int E = l.e_experts, EO = E + l.e_identity, K = l.e_top, lde = ld8(EO + 1), NH = glu ? 2 * l.e_ff : l.e_ff, ldh = ld8(NH),
+                      ldg = ld8(l.e_ff), ldw8 = ld8(W), lds = ld8(l.e_shared_ff);
+            const lcc::MoeRouterOpts ro{l.e_router_kind == LCC_ROUTER_SOFTMAX, l.e_identity, l.e_groups, l.e_keep};
+            const int up_act = glu ? lcc::ACT_NONE : lcc::ACT_RELU2;
             float* mf = (float*)(ws + L.moe_f);
             float* logit = mf; float* wsel = mf + (size_t)T * lde; float* sgate = wsel + (size_t)T * K;
             int* mi = (int*)(ws + L.moe_i);
             int* sel = mi; int* rank = sel + (size_t)T * K; int* posn = rank + (size_t)T * K; int* src_row = posn + (size_t)T * K;
             int* tile_group = src_row + L.moe_rows; int* counts = tile_group + L.moe_rows / kMoeTile + 1; int* row_off = counts + E;
-            uint8_t* ex = ws + L.moe_x; uint8_t* eh = ws + L.moe_h; uint8_t* eo = ws + L.moe_o;
-            const bool shared = l.e_shared_ff > 0;
+            uint8_t* ex = ws + L.moe_x; uint8_t* eh = ws + L.moe_h; uint8_t* eg = ws + L.moe_g; uint8_t* eo = ws + L.moe_o;
+            const bool shared = l.e_shared_ff > 0, ident = l.e_identity > 0;
+            float* gate_out = (shared || ident) ? sgate : nullptr;   // the shared expert's gate, or the chosen identity experts' weights
             // experts on the tensor cores: bf16, enough routed rows, 8-aligned shapes; lists are then padded to whole tiles
             const bool tc = m->use_tc && dt == LCC_DT_BF16 && T * K >= kMoeTcMinRows && (W % 8) == 0 && (l.e_ff % 8) == 0 && W >= 64 && l.e_ff >= 64;
             const int rows_max = T * K + E * (kMoeTile - 1), n_tiles = (rows_max + kMoeTile - 1) / kMoeTile;
@@ -560,33 +642,35 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
                 STEP(linear(m, mid2, lds, l.e_shared_down, nullptr, o2, W, false, T, W, l.e_shared_ff, ss), "shared expert down");
             }
             // router logits (and the shared expert's gate logit) accumulate in fp32 from the normed row
-            STEP(linear(m, xa, W, l.e_router, nullptr, logit, lde, true, T, E + (shared ? 1 : 0), W, s), "router");
-            if (!tc && T * K <= 256 && E <= 512) {
-                STEP(lcc::moe_route_small(logit, lde, l.e_correction_f32, E, K, l.e_scale, sel, wsel, shared ? sgate : nullptr, row_off, posn,
-                                          src_row, T, s), "expert choice + row lists");
+            STEP(linear(m, xa, W, l.e_router, nullptr, logit, lde, true, T, EO + (shared ? 1 : 0), W, s), "router");
+            if (!tc && T * K <= 256 && EO <= 512) {
+                STEP(lcc::moe_route_small(logit, lde, l.e_correction_f32, EO, K, l.e_scale, sel, wsel, gate_out, row_off, posn,
+                                          src_row, T, s, &ro), "expert choice + row lists");
             } else {
                 if (cudaMemsetAsync(counts, 0, sizeof(int) * E, s) != cudaSuccess) LCC_FAIL(m->ctx, -100, "router counters");
                 if (tc && cudaMemsetAsync(src_row, 0xff, sizeof(int) * (size_t)n_tiles * kMoeTile, s) != cudaSuccess) LCC_FAIL(m->ctx, -100, "row lists");
-                STEP(lcc::moe_route(logit, lde, l.e_correction_f32, E, K, l.e_scale, sel, wsel, shared ? sgate : nullptr, counts, rank, T, s), "expert choice");
+                STEP(lcc::moe_route(logit, lde, l.e_correction_f32, EO, K, l.e_scale, sel, wsel, gate_out, counts, rank, T, s, &ro), "expert choice");
                 STEP(lcc::moe_index(sel, rank, counts, E, K, tc ? kMoeTile : 1, row_off, posn, src_row, tc ? tile_group : nullptr, n_tiles, T, s), "expert row lists");
             }
             if (tc) {
                 STEP(lcc::moe_gather_rows(dt, xa, W, src_row, ex, ldw8, n_tiles * kMoeTile, W, s), "expert row gather");
                 lcc::GemmArgs a;
-                a.A = ex; a.B = l.e_up; a.C = eh; a.M = n_tiles * kMoeTile; a.N = l.e_ff; a.K = W; a.lda = ldw8; a.ldb = W; a.ldc = ldh;
-                a.bias = nullptr; a.residual = nullptr; a.ldr = 0; a.epi = lcc::EPI_RELU2; a.block_n = 0;
+                a.A = ex; a.B = l.e_up; a.C = eh; a.M = n_tiles * kMoeTile; a.N = NH; a.K = W; a.lda = ldw8; a.ldb = W; a.ldc = ldh;
+                a.bias = nullptr; a.residual = nullptr; a.ldr = 0; a.epi = glu ? lcc::EPI_NONE : lcc::EPI_RELU2; a.block_n = 0;
                 a.tile_group = tile_group; a.groups = E;
                 STEP(lcc::gemm_bf16_tn(a, m->ctx->num_sms, s), "experts up");
-                a.A = eh; a.B = l.e_down; a.C = eo; a.N = W; a.K = l.e_ff; a.lda = ldh; a.ldb = l.e_ff; a.ldc = ldw8; a.epi = lcc::EPI_NONE;
+                if (glu) STEP(lcc::glu_clamp_swish(dt, eh, ldh, eg, ldg, n_tiles * kMoeTile, l.e_ff, l.e_limit, s), "expert activation");
+                a.A = glu ? eg : eh; a.B = l.e_down; a.C = eo; a.N = W; a.K = l.e_ff; a.lda = glu ? ldg : ldh; a.ldb = l.e_ff; a.ldc = ldw8; a.epi = lcc::EPI_NONE;
                 STEP(lcc::gemm_bf16_tn(a, m->ctx->num_sms, s), "experts down");
             } else {
                 lcc::GroupedLinear g{};
                 g.dt = dt; g.A = xa; g.lda = W; g.a_stride = 0; g.a_rows = src_row; g.row_off = row_off; g.M_total = T * K;
-                g.W = l.e_up; g.ldw = W; g.w_stride = (int64_t)l.e_ff * W;
+                g.W = l.e_up; g.ldw = W; g.w_stride = (int64_t)NH * W;
                 g.C = eh; g.ldc = ldh; g.c_stride = 0; g.c_f32 = false;
-                g.groups = E; g.M = T; g.N = l.e_ff; g.K = W; g.act = lcc::ACT_RELU2;
+                g.groups = E; g.M = T; g.N = NH; g.K = W; g.act = up_act;
                 STEP(lcc::linear_grouped(g, s), "experts up");
-                g.A = eh; g.lda = ldh; g.a_rows = nullptr;
+                if (glu) STEP(lcc::glu_clamp_swish(dt, eh, ldh, eg, ldg, T * K, l.e_ff, l.e_limit, s), "expert activation");
+                g.A = glu ? eg : eh; g.lda = glu ? ldg : ldh; g.a_rows = nullptr;
                 g.W = l.e_down; g.ldw = l.e_ff; g.w_stride = (int64_t)W * l.e_ff;
                 g.C = eo; g.ldc = ldw8; g.N = W; g.K = l.e_ff; g.act = lcc::ACT_NONE;
                 STEP(lcc::linear_grouped(g, s), "experts down");
@@ -596,16 +680,27 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
             if (hc) {   // the weighted sum of the experts' rows is formed by the boundary kernel that folds it into the streams
                 pend_mc = lcc::MoeCombine{eo, ldw8, posn, wsel, K, shared ? o2 : nullptr, W, sgate};
                 pend_is_mc = true;
+            } else if (par) {   // ... or by the residual kernel that closes the layer; identity experts return the normed row
+                par_mc = lcc::MoeCombine{eo, ldw8, posn, wsel, K, shared ? (const void*)o2 : (ident ? (const void*)xa : nullptr), W, sgate};
+                par_is_mc = true;
             } else {
                 STEP(lcc::moe_combine(dt, eo, ldw8, posn, wsel, K, shared ? o2 : nullptr, W, sgate, o1, W, T, W, s), "expert combine");
             }
+        } else if (l.ff > 0 && l.ff_kind == LCC_FF_MLP) {
+            const int ldf = ld8(l.ff);
+            STEP(linear(m, xa, W, l.ff_in, nullptr, mid, ldf, false, T, l.ff, W, s, nullptr, lcc::ACT_GELU_TANH), "feed-forward up + gelu");
+            STEP(linear(m, mid, ldf, l.ff_out, nullptr, par ? o2 : o1, W, false, T, W, l.ff, s), "feed-forward down");
         } else if (l.ff > 0) {
             const int ldg = ld8(2 * l.ff), ldf = ld8(l.ff);
             STEP(linear(m, xa, W, l.ff_in, nullptr, proj, ldg, false, T, 2 * l.ff, W, s), "feed-forward in");
             STEP(lcc::glu_gelu_tanh(dt, proj, ldg, mid, ldf, T, l.ff, s), "gated gelu");
-            STEP(linear(m, mid, ldf, l.ff_out, nullptr, o1, W, false, T, W, l.ff, s), "feed-forward out");
+            STEP(linear(m, mid, ldf, l.ff_out, nullptr, par ? o2 : o1, W, false, T, W, l.ff, s), "feed-forward out");
         }
-        if (has_ff) {
+        if (par) {
+            // x <- x + (mixer + feed-forward), then the next layer's norm of the new row
+            STEP(lcc::residual_norm(dt, x32, o1, W, (has_ff && !par_is_mc) ? o2 : nullptr, W, par_is_mc ? &par_mc : nullptr, norm_of(li + 1),
+                                    xa, T, W, s), "residual sum + next norm");
+        } else if (has_ff) {
             if (hc) pend_hc = l.hc2_f32;
             else STEP(lcc::postnorm_residual(dt, x32, xa, o1, W, nullptr, nullptr, 0, nullptr, l.norm2_f32, d.alpha, d.eps, T, W, s), "norm2");
         }
@@ -620,9 +715,10 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
             LCC_FAIL(m->ctx, -100, "layer dump copy failed");
     }
     if (n_want > 0) {
-        STEP(lcc::gather_rmsnorm(dt, hc ? xsum : x32, want_rows, d.final_norm_f32, d.eps, xf, n_want, W, s), "final norm");
+        const lcc::NormSpec fn{d.norm_kind, d.final_norm_f32, d.final_norm_bias_f32, d.final_norm_alpha, d.eps};
+        STEP(lcc::gather_norm(dt, hc ? xsum : x32, want_rows, fn, xf, n_want, W, s), "final norm");
         STEP(lcc::linear_any(dt, xf, W, d.head, W, nullptr, logits, d.vocab, true, n_want, d.vocab, W, s), "output head");
-        STEP(lcc::softcap(logits, (int64_t)n_want * d.vocab, d.logit_softcap, s), "logit soft cap");
+        STEP(lcc::softcap(logits, (int64_t)n_want * d.vocab, d.logit_softcap, s, d.logit_scale != 0.f ? d.logit_scale : 1.f), "logit soft cap / scale");
         if (logits_copy &&
             cudaMemcpyAsync(logits_copy, logits, (size_t)n_want * d.vocab * 4, cudaMemcpyDeviceToDevice, s) != cudaSuccess)
             LCC_FAIL(m->ctx, -100, "logits copy failed");

@@ -7,7 +7,7 @@
 //   rotary.cu       rotate-half rotary positions on slices of a projection, packed to fp32 for a recurrence
 //   attn_latent.cu  latent (low-rank) K/V cache: latent norm + shared rotary key part -> pages, rotary query part
 //   hyper.cu        pre-norm blocks on several residual streams (hyper-connections)
-//   moe.cu          sigmoid top-k router, expert row lists, weighted combine
+//   moe.cu          sigmoid or softmax top-k router (groups of experts, identity experts), expert row lists, weighted combine
 // Every op exists for two storage types (DT_BF16: bf16 storage, fp32 arithmetic where the model asks for it;
 // DT_F32: everything fp32). All return 0 on success, negative on invalid arguments; launches are asynchronous on `s`.
 #pragma once
@@ -26,6 +26,13 @@ struct SeqPos {
     int past;
     const int* kv_len;
     const int* finished;
+};
+
+// The row a routed feed-forward contributes, formed inside the kernel that consumes it (hyper_boundary, residual_norm):
+//   y[r] = sum_k weight[r, k] * eo[pos[r, k]] + gate[r] * so[r]   (fp32; choices with pos < 0 are skipped)
+struct MoeCombine {
+    const void* eo; int ld_eo; const int* pos; const float* weight; int top;
+    const void* so; int ld_so; const float* gate;      // so null: no shared expert
 };
 
 // ---- linear_any.cu ------------------------------------------------------------------------------------------------------
@@ -48,7 +55,7 @@ struct GroupedLinear {
     const int* row_off; const int* a_rows; int M_total;
     int act;
 };
-enum { ACT_NONE = 0, ACT_RELU2 = 1 };
+enum { ACT_NONE = 0, ACT_RELU2 = 1, ACT_GELU_TANH = 2 };   // 2: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))
 int linear_grouped(const GroupedLinear& g, cudaStream_t s);
 
 // ---- recurrent.cu -------------------------------------------------------------------------------------------------------
@@ -127,6 +134,23 @@ int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_p
 // and merge the splits in the last CTA to arrive. key_hint: the host's estimate of the window (sets the number of splits
 // only; any length is computed correctly).
 size_t attn_split_ws_floats(int rows, int Hq, int DV);
+// Further options of attn_chunk_sink (null: chunks only, a zero-logit sink, one gate per head). window > 0: a row at position
+// i sees only j with i - j < window (inside its chunk, when there are chunks too). no_sink: ordinary softmax over the visible
+// keys. gate_channel: the gate slice is [S, Hq*DV], one sigmoid gate per output element.
+struct AttnOpts { int window; bool no_sink; bool gate_channel; };
+int attn_masked(int dt, const float* q, const void* k_pages, const void* v_pages, const int* page_table, int page_size,
+                const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D, int DV, int chunk, float scale,
+                bool tensor_cores, SeqPos pos, cudaStream_t s, const AttnOpts& opt, const float* sink = nullptr, int ld_v = 0,
+                float* split_ws = nullptr, size_t split_ws_floats = 0, int key_hint = 0);
+// Per-head RMS norm of q and k (weights qn_w, kn_w: fp32 [D], shared by the heads), then rotary positions on the first
+// rot_dims channels of every q and k head (rot_pairs: channel 2i turns with 2i+1, else i with i + rot_dims/2; angle =
+// position * inv_freq[i] in fp32, cos and sin times mag), then: q -> q_out fp32 [S, Hq*D]; k -> K pages; the values -> V
+// pages, read from columns [v_col, v_col + G*DV) of the row as projected (v_col = Hq*D: the values are the un-normed,
+// unrotated keys). proj: [S, ld] rows laid out [q: Hq*D | k: G*D | ...] (storage dt). Page layout as qk_norm_kv_append.
+int qk_headnorm_rope_append(int dt, const void* proj, int ld, int v_col, const float* qn_w, const float* kn_w, float eps,
+                            const float* inv_freq, float mag, int rot_dims, int rot_pairs, float* q_out, void* k_pages,
+                            void* v_pages, const int* page_table, int page_size, int S, int Hq, int G, int D, int DV, SeqPos pos,
+                            cudaStream_t s);
 
 // ---- rotary.cu ----------------------------------------------------------------------------------------------------------
 // Rotary positions in the rotate-half layout: inside a head, channel i < dims/2 of the rotated block pairs with channel
@@ -158,10 +182,6 @@ int latent_kv_append(int dt, const void* proj, int ld, int has_kv, const float* 
 // prev: fp32 [in: n | out: n | mix: n*n] of the sublayer that produced y; next: the same block of the sublayer that reads xa.
 // mc (instead of y): the finished sublayer is a routed feed-forward whose output row is formed here,
 //   y[r] = sum_k weight[r, k] * eo[pos[r, k]] + gate[r] * so[r]   (in fp32; moe_combine as part of the boundary).
-struct MoeCombine {
-    const void* eo; int ld_eo; const int* pos; const float* weight; int top;
-    const void* so; int ld_so; const float* gate;      // so null: no shared expert
-};
 int hyper_boundary(int dt, float* xs, int n, const void* y, int ld_y, const float* prev, const float* next, const float* w,
                    float eps, void* xa, float* sum_out, int S, int W, cudaStream_t s, const MoeCombine* mc = nullptr);
 
@@ -171,13 +191,19 @@ int hyper_boundary(int dt, float* xs, int n, const void* y, int ld_y, const floa
 // index), weight = score * scale (no renormalisation). Outputs: sel int32 [S, top], weight fp32 [S, top],
 // shared_gate fp32 [S] = sigmoid(logit[E]) (when shared_gate is non-null); counts int32 [E] must be zero on entry and
 // receives the number of rows per expert; rank int32 [S, top] = the row's arrival number inside its expert.
+// opt (null: a sigmoid score per expert, no identity experts, no groups): softmax: score = softmax over all E router outputs;
+// identity: the last `identity` of the E outputs stand for experts that return their input: they enter no list (rank and pos
+// are -1, counts / row_off cover the E - identity real experts) and the sum of their weights goes to shared_gate[r] (which
+// must then be given; the logits have no shared-gate column); groups > 0: the E outputs form that many equal groups of
+// neighbours, a group scores as its largest choice score and only members of the `keep` best groups can be chosen.
+struct MoeRouterOpts { bool softmax; int identity; int groups; int keep; };
 int moe_route(const float* logits, int ld, const float* correction, int E, int top, float scale, int* sel, float* weight,
-              float* shared_gate, int* counts, int* rank, int S, cudaStream_t s);
+              float* shared_gate, int* counts, int* rank, int S, cudaStream_t s, const MoeRouterOpts* opt = nullptr);
 // moe_route and moe_index (dense lists) in one launch of one CTA, for calls of up to kMoeSmallItems (row, choice) pairs; it
 // needs no counters.
 constexpr int kMoeSmallItems = 1024;
 int moe_route_small(const float* logits, int ld, const float* correction, int E, int top, float scale, int* sel, float* weight,
-                    float* shared_gate, int* row_off, int* pos, int* src_row, int S, cudaStream_t s);
+                    float* shared_gate, int* row_off, int* pos, int* src_row, int S, cudaStream_t s, const MoeRouterOpts* opt = nullptr);
 // Expert-sorted row lists. Each list is padded to a multiple of `pad` rows (1: dense). row_off int32 [E+1] = start of every
 // list (row_off[E] = total); pos[r, k] = row_off[sel] + rank = the row's place; src_row[pos] = r (entries of padding rows
 // are not written: fill src_row with -1 first when pad > 1). tile_group (optional, int32 [n_tiles]): the list that owns
@@ -186,7 +212,8 @@ int moe_index(const int* sel, const int* rank, const int* counts, int E, int top
               int* tile_group, int n_tiles, int S, cudaStream_t s);
 // out[i, :] = in[src_row[i], :] for rows with src_row[i] >= 0 (storage dt; W, leading dimensions and bases 16-byte aligned)
 int moe_gather_rows(int dt, const void* in, int ld_in, const int* src_row, void* out, int ld_out, int rows, int W, cudaStream_t s);
-// out[r, :] = sum_k weight[r, k] * eo[pos[r, k], :] (+ shared_gate[r] * so[r, :])   (eo, so, out: storage dt)
+// out[r, :] = sum_k weight[r, k] * eo[pos[r, k], :] (+ shared_gate[r] * so[r, :])   (eo, so, out: storage dt); choices with
+// pos < 0 (identity experts) are skipped: their share is the so term
 int moe_combine(int dt, const void* eo, int ld_eo, const int* pos, const float* weight, int top, const void* so, int ld_so,
                 const float* shared_gate, void* out, int ld_out, int S, int W, cudaStream_t s);
 
@@ -209,7 +236,20 @@ int glu_gelu_tanh(int dt, const void* gu, int ld, void* out, int ld_out, int S, 
 // out[i, :] = rms(x32[rows[i], :]) * w  (storage dt)
 int gather_rmsnorm(int dt, const float* x32, const int* rows, const float* w, float eps, void* out, int n_rows, int W,
                    cudaStream_t s);
-// x <- cap * tanh(x / cap) in place (fp32); cap <= 0: unchanged
-int softcap(float* x, int64_t n, float cap, cudaStream_t s);
+// A row norm: NORM_RMS x / sqrt(mean(x^2) + eps) * w; NORM_DYT tanh(alpha * x) * w + b (no statistics of the row).
+enum { NORM_RMS = 0, NORM_DYT = 1 };
+struct NormSpec { int kind; const float* w; const float* b; float alpha; float eps; };
+// out[i, :] = norm(x32[rows[i], :])  (storage dt)
+int gather_norm(int dt, const float* x32, const int* rows, const NormSpec& n, void* out, int n_rows, int W, cudaStream_t s);
+// End of a parallel block (both sublayers read the same normed row) fused with the next block's norm:
+//   x32 <- x32 + (a + b)  in fp32 (a, b: [S, W] storage dt, either may be null; mc instead of b: the routed feed-forward's row
+//   sum_k weight[r, k] * eo[pos[r, k]] + gate[r] * so[r] is formed here in fp32), then, if next.w, xa = next(x32) (storage dt).
+// mc->so may be xa itself (identity experts return the block's normed input): every element is read before it is rewritten.
+int residual_norm(int dt, float* x32, const void* a, int ld_a, const void* b, int ld_b, const MoeCombine* mc, const NormSpec& next,
+                  void* xa, int S, int W, cudaStream_t s);
+// out[r, c] = g * sigmoid(1.702 g) * (u + 1), g = min(gu[r, c], limit), u = clamp(gu[r, F + c], -limit, limit)
+int glu_clamp_swish(int dt, const void* gu, int ld, void* out, int ld_out, int S, int F, float limit, cudaStream_t s);
+// x <- cap * tanh(x / cap) in place (fp32; cap <= 0: unchanged), then x <- x * scale
+int softcap(float* x, int64_t n, float cap, cudaStream_t s, float scale = 1.f);
 
 }  // namespace lcc

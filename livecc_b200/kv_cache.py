@@ -197,7 +197,8 @@ class SeqStatePool(PageAllocator):
       reads another layer's cache has no entry here.
     * Recurrent layers: one fp32 slot per sequence and layer (`state_floats[i]` elements, 0 for none), zeroed when a
       sequence takes it.
-    attn_layers: {layer index: (kv_heads, dim, vdim, chunk)}; state_floats: per layer."""
+    attn_layers: {layer index: (kv_heads, dim, vdim, chunk[, window])}; state_floats: per layer. A layer with a sliding
+    window of w positions never looks more than w - 1 positions behind the newest token."""
 
     def __init__(self, attn_layers: dict, state_floats: List[int], dtype, device, initial_pages: int = 32, initial_slots: int = 2):
         self.attn_layers = dict(attn_layers)
@@ -214,7 +215,7 @@ class SeqStatePool(PageAllocator):
 
     # pages ------------------------------------------------------------------------------------
     def _resize_storage(self, new_total: int):
-        for i, (g, d, dv, _chunk) in self.attn_layers.items():
+        for i, (g, d, dv, *_mask) in self.attn_layers.items():
             k = torch.zeros((new_total, g, PAGE_SIZE, d), dtype=self.dtype, device=self.device)
             v = torch.zeros((new_total, g, PAGE_SIZE, dv), dtype=self.dtype, device=self.device) if dv else None
             if self.k[i] is not None:
@@ -228,8 +229,11 @@ class SeqStatePool(PageAllocator):
         if not self.attn_layers:
             return seq_len
         lo = seq_len
-        for (_g, _d, _dv, chunk) in self.attn_layers.values():
-            lo = min(lo, (seq_len // chunk) * chunk if chunk > 0 else 0)
+        for (_g, _d, _dv, chunk, *rest) in self.attn_layers.values():
+            first = (seq_len // chunk) * chunk if chunk > 0 else 0
+            if rest and rest[0] > 0:       # the next token sits at position seq_len and sees seq_len - window + 1 onwards
+                first = max(first, seq_len - rest[0] + 1)
+            lo = min(lo, first)
         return lo
 
     # state slots ------------------------------------------------------------------------------
@@ -259,7 +263,7 @@ class SeqStatePool(PageAllocator):
 
     def bytes_per_token(self) -> int:
         es = torch.empty((), dtype=self.dtype).element_size()
-        return sum(g * (d + dv) * es for (g, d, dv, _c) in self.attn_layers.values())
+        return sum(g * (d + dv) * es for (g, d, dv, *_m) in self.attn_layers.values())
 
     def state_bytes_per_sequence(self) -> int:
         return 4 * sum(self.state_floats)

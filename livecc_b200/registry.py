@@ -23,6 +23,7 @@ register("Qwen2VLForConditionalGeneration", "livecc_b200.engine", "LiveCCB200For
 register("qwen2_vl", "livecc_b200.engine", "LiveCCB200ForConditionalGeneration")
 register("Bimopel", "livecc_b200.seq_engine", "SeqLMForCausalLM")
 register("Kedelorn", "livecc_b200.seq_engine", "SeqLMForCausalLM")
+register("Dibedra", "livecc_b200.seq_engine", "SeqLMForCausalLM")
 
 
 def architectures() -> list:

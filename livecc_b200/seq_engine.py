@@ -75,10 +75,21 @@ class SeqWeights:
             freq, mag = rot.frequencies()
             return torch.tensor(freq, dtype=torch.float64).to(torch.float32).to(device), float(mag)
 
+        dyt = cfg.norm == "dyt"
+
+        def norm_extra(name):   # a Dynamic-Tanh norm keeps a bias vector and a scalar beside its weight
+            if not dyt:
+                return None, 0.0
+            check(name + ".b", (W,))
+            if get(name + ".alpha").numel() != 1:
+                raise ValueError(f"{name}.alpha is not a scalar")
+            return f32(get(name + ".b")), float(get(name + ".alpha").to(torch.float32).reshape(-1)[0])
+
         W = cfg.width
         self.embed = mat("embed")
         self.head = mat("head")
         self.final_norm = norm_w("final.norm")
+        self.final_norm_bias, self.final_norm_alpha = norm_extra("final.norm")
         if shape("embed") != (cfg.vocab, W) or shape("head") != (cfg.vocab, W):
             raise ValueError("embed / head do not have the shape [vocab, width] of config.json")
         self.inv_freq = None
@@ -88,8 +99,12 @@ class SeqWeights:
         hc = cfg.block == "prenorm_hc"
         self.layers: List[dict] = []
         for i, L in enumerate(cfg.layers):
+            if L.weights_of >= 0:            # the layer runs with another layer's tensors (its cache and state are its own)
+                self.layers.append(self.layers[L.weights_of])
+                continue
             p = f"l{i}."
             w = {"norm1": norm_w(p + "norm1")}
+            w["norm1_bias"], w["norm1_alpha"] = norm_extra(p + "norm1")
             if hc:
                 n = cfg.streams
                 for q in ("hc1", "hc2") if (L.ff or L.moe) else ("hc1",):
@@ -125,6 +140,22 @@ class SeqWeights:
                 w["a_sink"] = f32(get(m + "sink"))
                 w["a_out"] = mat(m + "o")
                 w["rot_freq"], w["rot_mag"] = rotary(a.rot)
+            elif L.type == "attention":
+                a, m = L.attn, p + "mix."
+                check(m + "q", (a.heads * a.dim, W)), check(m + "k", (a.kv_heads * a.dim, W)), check(m + "o", (W, a.heads * a.vdim))
+                check(m + "q.norm", (a.dim,)), check(m + "k.norm", (a.dim,))
+                rows = [m + "q", m + "k"]
+                if not a.value_keys:
+                    check(m + "v", (a.kv_heads * a.vdim, W))
+                    rows.append(m + "v")
+                if a.gate != "none":
+                    check(m + "g", (a.gate_rows, W))
+                    rows.append(m + "g")
+                w["m_in"] = mat(*rows)
+                w["m_qnorm"], w["m_knorm"] = f32(get(m + "q.norm")), f32(get(m + "k.norm"))
+                w["m_out"] = mat(m + "o")
+                if a.rot.dims:
+                    w["rot_freq"], w["rot_mag"] = rotary(a.rot)
             elif L.type == "mamba2":
                 s = L.ssd
                 m = p + "mix."
@@ -167,13 +198,21 @@ class SeqWeights:
                 w["r_norm"] = f32(get(b + "norm"))
                 w["r_out"] = mat(b + "o")
                 w["r_branch_norm"] = f32(get(b + "out"))
+            par = cfg.block == "parallel"      # one norm per layer: the feed-forward reads the mixer's input
             if L.moe:
                 e, m = L.moe, p + "mlp."
-                w["norm2"] = norm_w(p + "norm2")
+                if not par:
+                    w["norm2"] = norm_w(p + "norm2")
                 for j in range(e.experts):
                     check(f"{m}e{j}.up", (e.ff, W)), check(f"{m}e{j}.down", (W, e.ff))
-                check(m + "router", (e.experts, W)), check(m + "correction", (e.experts,))
-                w["e_up"] = torch.stack([get(f"{m}e{j}.up") for j in range(e.experts)]).to(device=device, dtype=dtype).contiguous()
+                check(m + "router", (e.outputs, W)), check(m + "correction", (e.outputs,))
+                if e.act == "clamp_glu":     # each expert's gate rows, then its up rows: one product per expert list
+                    for j in range(e.experts):
+                        check(f"{m}e{j}.gate", (e.ff, W))
+                    w["e_up"] = torch.stack([torch.cat([get(f"{m}e{j}.gate"), get(f"{m}e{j}.up")], 0) for j in range(e.experts)]) \
+                        .to(device=device, dtype=dtype).contiguous()
+                else:
+                    w["e_up"] = torch.stack([get(f"{m}e{j}.up") for j in range(e.experts)]).to(device=device, dtype=dtype).contiguous()
                 w["e_down"] = torch.stack([get(f"{m}e{j}.down") for j in range(e.experts)]).to(device=device, dtype=dtype).contiguous()
                 w["e_correction"] = f32(get(m + "correction"))
                 if e.shared_ff:
@@ -183,17 +222,22 @@ class SeqWeights:
                 else:
                     w["e_router"] = mat(m + "router")
             elif L.ff:
-                w["norm2"] = norm_w(p + "norm2")
-                w["ff_in"] = mat(p + "mlp.gate", p + "mlp.up")
+                if not par:
+                    w["norm2"] = norm_w(p + "norm2")
+                check(p + "mlp.up", (L.ff, W)), check(p + "mlp.down", (W, L.ff))
+                if cfg.dense == "mlp":
+                    w["ff_in"] = mat(p + "mlp.up")
+                else:
+                    check(p + "mlp.gate", (L.ff, W))
+                    w["ff_in"] = mat(p + "mlp.gate", p + "mlp.up")
                 w["ff_out"] = mat(p + "mlp.down")
-                if shape(p + "mlp.gate") != (L.ff, W) or shape(p + "mlp.up") != (L.ff, W):
-                    raise ValueError(f"layer {i}: feed-forward width does not match config.json")
             self.layers.append(w)
         self.unused = sorted(set(t) - used)
 
     def nbytes(self) -> int:
         n = sum(x.numel() * x.element_size() for x in (self.embed, self.head, self.final_norm))
-        return n + sum(x.numel() * x.element_size() for w in self.layers for x in w.values() if isinstance(x, torch.Tensor))
+        own = {id(w): w for w in self.layers}.values()      # layers that share tensors count once
+        return n + sum(x.numel() * x.element_size() for w in own for x in w.values() if isinstance(x, torch.Tensor))
 
 
 class SeqLMForCausalLM:
@@ -208,6 +252,8 @@ class SeqLMForCausalLM:
         self.ctx = _cabi.Context(device.index if device.index is not None else torch.cuda.current_device(), profile=self.PROFILE)
         self._native = self._build_native()
         attn = {i: (L.left.kv_heads, L.left.dim, L.left.vdim, L.left.chunk) for i, L in enumerate(config.layers) if L.type == "parallel"}
+        # sliding-window attention: (kv heads, key size, value size, no chunks, window)
+        attn.update({i: (L.attn.kv_heads, L.attn.dim, L.attn.vdim, 0, L.attn.window) for i, L in enumerate(config.layers) if L.type == "attention"})
         # a latent cache is one K pool of [latent | rotary key part] rows; a layer that reads another layer's cache has none
         attn.update({i: (1, L.latent.kv_rank + L.latent.rot_dim, 0, 0) for i, L in enumerate(config.layers)
                      if L.type == "latent_attention" and L.latent.kv_from < 0})
@@ -247,6 +293,7 @@ class SeqLMForCausalLM:
             e = arr[i]
             e.ff = L.ff
             e.norm1_f32 = p(lw["norm1"])
+            e.norm1_bias_f32, e.norm1_alpha = p(lw.get("norm1_bias")), lw.get("norm1_alpha", 0.0)
             e.hc1_f32, e.hc2_f32 = p(lw.get("hc1")), p(lw.get("hc2"))
             e.a_kv_from = -1
             e.rot_inv_freq_f32, e.rot_mag = p(lw.get("rot_freq")), lw.get("rot_mag", 1.0)
@@ -262,6 +309,14 @@ class SeqLMForCausalLM:
                 e.a_scale = a.scale
                 e.a_in, e.a_latent_norm_f32, e.a_uk_t, e.a_uv = p(lw["a_in"]), p(lw.get("a_latent_norm")), p(lw["a_uk_t"]), p(lw["a_uv"])
                 e.a_sink_f32, e.a_out = p(lw["a_sink"]), p(lw["a_out"])
+            elif L.type == "attention":
+                a = L.attn
+                e.type = _cabi.MIX_ATTENTION
+                e.m_heads, e.m_kv_heads, e.m_dim, e.m_vdim, e.m_window, e.m_chunk = a.heads, a.kv_heads, a.dim, a.vdim, a.window, 0
+                e.m_rot_dims, e.m_rot_pairs, e.m_sink, e.m_value_keys = a.rot.dims, int(a.rot_pairs), int(a.sink), int(a.value_keys)
+                e.m_gate = {"none": _cabi.GATE_NONE, "head": _cabi.GATE_HEAD, "channel": _cabi.GATE_CHANNEL}[a.gate]
+                e.m_scale = a.scale
+                e.m_in, e.m_qnorm_f32, e.m_knorm_f32, e.m_out = p(lw["m_in"]), p(lw["m_qnorm"]), p(lw["m_knorm"]), p(lw["m_out"])
             elif L.type == "mamba2":
                 s = L.ssd
                 e.type = _cabi.MIX_SSD
@@ -283,16 +338,22 @@ class SeqLMForCausalLM:
                 x = L.moe
                 e.ff_kind = _cabi.FF_MOE
                 e.e_experts, e.e_top, e.e_ff, e.e_shared_ff, e.e_scale = x.experts, x.top, x.ff, x.shared_ff, x.scale
-                e.norm2_f32, e.e_router, e.e_correction_f32 = p(lw["norm2"]), p(lw["e_router"]), p(lw["e_correction"])
+                e.e_router_kind = _cabi.ROUTER_SOFTMAX if x.router == "softmax" else _cabi.ROUTER_SIGMOID
+                e.e_identity, e.e_groups, e.e_keep, e.e_limit = x.identity, x.groups, x.keep, x.limit
+                e.e_act = _cabi.EXPERT_CLAMP_GLU if x.act == "clamp_glu" else _cabi.EXPERT_RELU2
+                e.norm2_f32, e.e_router, e.e_correction_f32 = p(lw.get("norm2")), p(lw["e_router"]), p(lw["e_correction"])
                 e.e_up, e.e_down = p(lw["e_up"]), p(lw["e_down"])
                 e.e_shared_up, e.e_shared_down = p(lw.get("e_shared_up")), p(lw.get("e_shared_down"))
             elif L.ff:
-                e.norm2_f32, e.ff_in, e.ff_out = p(lw["norm2"]), p(lw["ff_in"]), p(lw["ff_out"])
+                e.ff_kind = _cabi.FF_MLP if cfg.dense == "mlp" else _cabi.FF_GLU
+                e.norm2_f32, e.ff_in, e.ff_out = p(lw.get("norm2")), p(lw["ff_in"]), p(lw["ff_out"])
         desc = _cabi.SeqModelDesc(
             width=cfg.width, vocab=cfg.vocab, n_layers=len(cfg.layers),
             dtype=_cabi.DT_F32 if self.dtype == torch.float32 else _cabi.DT_BF16, rows_padded8=1, eps=cfg.eps, alpha=cfg.alpha,
             embed_scale=cfg.embed_scale, logit_softcap=cfg.logit_softcap,
-            block=_cabi.BLOCK_PRENORM_HC if cfg.block == "prenorm_hc" else _cabi.BLOCK_POSTNORM, streams=cfg.streams,
+            block={"prenorm_hc": _cabi.BLOCK_PRENORM_HC, "parallel": _cabi.BLOCK_PARALLEL}.get(cfg.block, _cabi.BLOCK_POSTNORM), streams=cfg.streams,
+            norm_kind=_cabi.NORM_DYT if cfg.norm == "dyt" else _cabi.NORM_RMS, final_norm_alpha=w.final_norm_alpha,
+            logit_scale=cfg.logit_scale, final_norm_bias_f32=p(w.final_norm_bias),
             embed=p(w.embed), inv_freq_f32=p(w.inv_freq),
             final_norm_f32=p(w.final_norm), head=p(w.head), layers=arr)
         return _cabi.SeqNativeModel(self.ctx, desc, keepalive=(arr, w))
