@@ -298,7 +298,7 @@ def write_safetensors(path: str, tensors: Dict[str, torch.Tensor]) -> None:
     names = {v: k for k, v in _ST_DTYPES.items()}
     meta, blobs, off = {}, [], 0
     for name, t in tensors.items():
-        b = t.detach().cpu().contiguous().view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        b = t.detach().cpu().contiguous().reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""   # (scalars: one element)
         meta[name] = {"dtype": names[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(b)]}
         blobs.append(b)
         off += len(b)

@@ -248,7 +248,7 @@ lcc_seq_model* lcc_seq_model_create(lcc_ctx* ctx, const lcc_seq_model_desc* desc
     for (int i = 0; i < desc->n_layers; ++i) {
         const lcc_seq_layer& l = desc->layers[i];
         if (l.ff_kind == LCC_FF_MOE) {
-            if (l.e_experts < 1 || l.e_experts > 512 || l.e_top < 1 || l.e_top > l.e_experts || l.e_ff < 1 || l.e_shared_ff < 0)
+            if (l.e_experts < 1 || l.e_experts > 512 || l.e_top < 1 || l.e_top > l.e_experts + std::max(l.e_identity, 0) || l.e_ff < 1 || l.e_shared_ff < 0)
                 return fail("routed feed-forward: unsupported sizes");
             if ((!par && !l.norm2_f32) || !l.e_router || !l.e_correction_f32 || !l.e_up || !l.e_down || (l.e_shared_ff > 0 && (!l.e_shared_up || !l.e_shared_down)))
                 return fail("routed feed-forward: missing weights");

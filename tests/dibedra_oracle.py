@@ -158,3 +158,11 @@ def forward(config, tensors, ids, layer_dump=False, **kw):
     h = dyt(x, t["final.norm"], t["final.norm.b"], t["final.norm.alpha"])
     logits = (h @ t["head"].T) * float(config.get("logit_scale", 1.0))
     return (logits, torch.stack(dump)) if layer_dump else logits
+
+
+def greedy(config, tensors, prompt, n):
+    """n greedy tokens after `prompt` (the whole sequence is recomputed for every token)."""
+    seq = list(prompt)
+    for _ in range(n):
+        seq.append(int(forward(config, tensors, seq)[-1].argmax()))
+    return seq[len(prompt):]
