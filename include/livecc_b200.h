@@ -360,6 +360,8 @@ typedef struct {
      * their input; e_groups > 0: the router outputs form e_groups equal groups of neighbours and only the e_keep groups with the
      * largest choice score can be chosen; e_act LCC_EXPERT_*, e_limit its clamp */
     int32_t e_router_kind, e_identity, e_groups, e_keep, e_act;
+    int32_t e_up_il16; /* LCC_EXPERT_CLAMP_GLU: non-zero when each expert's gate and up rows are interleaved in groups of 16 (16 gate
+                          rows, then the 16 matching up rows; e_ff a multiple of 16) instead of [gate: e_ff | up: e_ff] */
     float e_limit;
     float norm1_alpha; /* LCC_NORM_DYT: the scalar inside tanh */
     /* weights: matrices [out, in] in the model's storage type; everything named *_f32 is fp32 */

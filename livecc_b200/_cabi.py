@@ -75,7 +75,7 @@ class SeqLayer(C.Structure):
                [(n, C.c_int32) for n in ("m_heads", "m_kv_heads", "m_dim", "m_vdim", "m_window", "m_chunk", "m_rot_dims", "m_rot_pairs",
                                          "m_sink", "m_value_keys", "m_gate")] + [("m_scale", C.c_float)] + \
                [(n, C.c_int32) for n in ("ff_kind", "e_experts", "e_top", "e_ff", "e_shared_ff")] + [("e_scale", C.c_float)] + \
-               [(n, C.c_int32) for n in ("e_router_kind", "e_identity", "e_groups", "e_keep", "e_act")] + \
+               [(n, C.c_int32) for n in ("e_router_kind", "e_identity", "e_groups", "e_keep", "e_act", "e_up_il16")] + \
                [("e_limit", C.c_float), ("norm1_alpha", C.c_float)] + \
                [(n, C.c_void_p) for n in ("norm1_f32", "norm2_f32", "norm1_bias_f32", "m_in", "m_qnorm_f32", "m_knorm_f32", "m_out", "s_in", "s_conv_w_f32", "s_conv_b_f32", "s_dt_bias_f32",
                                           "s_a_log_f32", "s_skip_f32", "s_norm_f32", "s_out", "l_in", "l_in_bias_f32", "l_in_bias",

@@ -43,7 +43,8 @@ __device__ __forceinline__ float gate_of(const T* gate, int ld_gate, int t, int 
     return 1.f / (1.f + expf(-z));
 }
 
-// One CTA per new row, one warp per head in turn (query heads, then key heads). Per head: sum of squares over D -> the
+// One CTA per (new row, slice of the heads): one warp per head in turn (query heads, then key heads; few-row steps spread a
+// row's heads over several CTAs). Per head: sum of squares over D -> the
 // normed channels -> rotation of the first rot_dims channels -> q_out, or the K page; the V page takes its columns of the
 // row as they are.
 template <typename T>
@@ -62,7 +63,7 @@ __global__ void __launch_bounds__(256) qk_headnorm_rope_append_kernel(const T* _
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int page = page_table[p / page_size], slot = p % page_size;
     const int half = rot_dims >> 1;
-    for (int hd = warp; hd < Hq + G; hd += nwarps) {
+    for (int hd = blockIdx.y * nwarps + warp; hd < Hq + G; hd += gridDim.y * nwarps) {
         const bool is_q = hd < Hq;
         const T* x = row + (size_t)hd * D;                 // k heads follow the q heads in the row
         const float* w = is_q ? qn_w : kn_w;
@@ -89,7 +90,7 @@ __global__ void __launch_bounds__(256) qk_headnorm_rope_append_kernel(const T* _
         }
     }
     const int nv = G * DV;
-    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < nv; i += gridDim.y * blockDim.x) {
         const int g = i / DV, d = i % DV;
         v_pages[(((size_t)page * G + g) * page_size + slot) * DV + d] = row[v_col + i];
     }
@@ -898,12 +899,15 @@ int qk_headnorm_rope_append(int dt, const void* proj, int ld, int v_col, const f
         rot_dims < 0 || (rot_dims & 1) || rot_dims > D || (rot_dims > 0 && !inv_freq) || v_col < 0 || v_col + G * DV > ld)
         return -2;
     count_launch();
+    // many rows: 8 warps walk a row's heads; few rows: 4-warp CTAs, one head per warp, so that a decode step fills more SMs
+    const int threads = S >= 64 ? 256 : 128;
+    const dim3 grid(S, S >= 64 ? 1 : (Hq + G + 3) / 4);
     if (dt == DT_F32)
-        qk_headnorm_rope_append_kernel<float><<<S, 256, 0, s>>>((const float*)proj, ld, v_col, qn_w, kn_w, eps, inv_freq, mag, rot_dims,
+        qk_headnorm_rope_append_kernel<float><<<grid, threads, 0, s>>>((const float*)proj, ld, v_col, qn_w, kn_w, eps, inv_freq, mag, rot_dims,
                                                                 rot_pairs, q_out, (float*)k_pages, (float*)v_pages, page_table, page_size,
                                                                 S, Hq, G, D, DV, pos);
     else
-        qk_headnorm_rope_append_kernel<bf16><<<S, 256, 0, s>>>((const bf16*)proj, ld, v_col, qn_w, kn_w, eps, inv_freq, mag, rot_dims,
+        qk_headnorm_rope_append_kernel<bf16><<<grid, threads, 0, s>>>((const bf16*)proj, ld, v_col, qn_w, kn_w, eps, inv_freq, mag, rot_dims,
                                                                rot_pairs, q_out, (bf16*)k_pages, (bf16*)v_pages, page_table, page_size,
                                                                S, Hq, G, D, DV, pos);
     return cudaGetLastError() == cudaSuccess ? 0 : -100;

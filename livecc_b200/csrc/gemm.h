@@ -18,12 +18,14 @@ enum GemmEpilogue {
     EPI_PARTIAL_F32 = 7,     // internal (split-K): fp32 partial tiles, reduced by splitk_reduce_kernel
     EPI_RELU2 = 8,           // C = bf16(relu(acc)^2)
     EPI_GELU_TANH = 9,       // C = bf16(gelu_tanh(acc)), the activation in fp32 on the accumulator
+    EPI_CLAMP_GLU = 10,      // gate/up rows interleaved by 16 as for EPI_SWIGLU: g = min(gate, limit), u = clamp(up, +-limit),
+                             // C[:, j] = bf16(g * sigmoid(1.702 g) * (u + 1)) in fp32 on the accumulators; limit = epi_param
 };
 
 struct GemmArgs {
     const void* A;  // [M, K] bf16, row stride lda
     const void* B;  // [N, K] bf16, row stride ldb   (nn.Linear weight layout)
-    void* C;        // [M, N] bf16 (EPI_SWIGLU: [M, N/2]), row stride ldc
+    void* C;        // [M, N] bf16 (EPI_SWIGLU, EPI_CLAMP_GLU: [M, N/2]), row stride ldc
     int M, N, K;
     int lda, ldb, ldc;
     const void* bias;      // [N] bf16 or null
@@ -47,6 +49,7 @@ struct GemmArgs {
     int a_col_stride = 0, c_col_stride = 0;
     // fp32 output: C is float [M, ldc] (ldc a multiple of 4), epi must be EPI_NONE
     bool c_f32 = false;
+    float epi_param = 0.f;   // EPI_CLAMP_GLU: the clamp
 };
 
 int gemm_bf16_tn(const GemmArgs& a, int num_sms, cudaStream_t stream);

@@ -16,6 +16,7 @@
 // overlaps the main loop of tile i+1.
 //
 // The fused epilogues reproduce the reference's bf16 rounding points (one torch op = one rounding).
+#include <string.h>
 #include <stdlib.h>
 
 #include "common.cuh"
@@ -94,6 +95,28 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&v)[32], bf16* C,
                 float g0 = rbf(__uint_as_float(v[2 * j])), g1 = rbf(__uint_as_float(v[2 * j + 1]));
                 float u0 = rbf(__uint_as_float(v[16 + 2 * j])), u1 = rbf(__uint_as_float(v[16 + 2 * j + 1]));
                 o[j] = pack_bf16x2(silu_bf16(g0) * u0, silu_bf16(g1) * u1);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(C + (size_t)row * ldc + ocol0);
+            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+    } else if (EPI == EPI_CLAMP_GLU) {
+        // the same 32-row interleave; the activation runs in fp32 on the accumulators and is rounded once. The clamp rides in
+        // the (otherwise unused) residual stride as float bits.
+        if (row_ok && col0 < tile_end) {
+            const float limit = __int_as_float(ldr);
+            const int ocol0 = (col0 >> 5) << 4;
+            uint32_t o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float y[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const float g = fminf(__uint_as_float(v[2 * j + e]), limit);
+                    const float u = fminf(fmaxf(__uint_as_float(v[16 + 2 * j + e]), -limit), limit);
+                    y[e] = g / (1.f + __expf(-1.702f * g)) * (u + 1.f);
+                }
+                o[j] = pack_bf16x2(y[0], y[1]);
             }
             uint4* dst = reinterpret_cast<uint4*>(C + (size_t)row * ldc + ocol0);
             dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
@@ -557,9 +580,11 @@ static int launch_cfg(const GemmArgs& a, int bn, int num_sms, cudaStream_t strea
     const int tiles = m_tiles * n_tiles * splits * batch;
     const int grid = tiles < num_sms ? tiles : num_sms;
     lcc::count_launch();
+    int ldr = a.ldr;
+    if (EPI == EPI_CLAMP_GLU) memcpy(&ldr, &a.epi_param, sizeof(int));   // no residual in this epilogue: the slot carries the clamp
     kern<<<grid, 384, cfg.smem_bytes, stream>>>(ta, tb, (bf16*)a.C, a.M, a.N, a.K, a.ldc,
                                                 (const bf16*)a.bias, (const bf16*)a.residual,
-                                                a.ldr, splits, cfg, a.tile_group, batch, a.a_col_stride, a.c_col_stride);
+                                                ldr, splits, cfg, a.tile_group, batch, a.a_col_stride, a.c_col_stride);
     return cudaGetLastError() == cudaSuccess ? 0 : -13;
 }
 
@@ -606,6 +631,7 @@ static int launch_epi(const GemmArgs& a, int bn, int num_sms, cudaStream_t strea
         case EPI_SWIGLU: return launch_cfg<EPI_SWIGLU>(a, bn, num_sms, stream);
         case EPI_RELU2: return launch_cfg<EPI_RELU2>(a, bn, num_sms, stream);
         case EPI_GELU_TANH: return launch_cfg<EPI_GELU_TANH>(a, bn, num_sms, stream);
+        case EPI_CLAMP_GLU: return launch_cfg<EPI_CLAMP_GLU>(a, bn, num_sms, stream);
     }
     return -14;
 }
@@ -721,7 +747,7 @@ static int try_splitk(const GemmArgs& a, int num_sms, cudaStream_t stream) {
 int gemm_bf16_tn(const GemmArgs& a, int num_sms, cudaStream_t stream) {
     if (a.M <= 0 || a.N <= 0 || a.K <= 0) return -1;
     if ((a.K % 8) || (a.lda % 8) || (a.ldb % 8) || (a.N % 8) || (a.ldc % (a.c_f32 ? 4 : 8))) return -2;
-    if (a.epi == EPI_SWIGLU && (a.N % 32)) return -3;
+    if ((a.epi == EPI_SWIGLU || a.epi == EPI_CLAMP_GLU) && (a.N % 32)) return -3;
     if ((a.epi == EPI_RESIDUAL || a.epi == EPI_BIAS_RESIDUAL) && (!a.residual || (a.ldr % 8))) return -4;
     if ((a.epi == EPI_BIAS || a.epi == EPI_BIAS_QUICKGELU || a.epi == EPI_BIAS_GELU ||
          a.epi == EPI_BIAS_RESIDUAL) && !a.bias) return -5;
@@ -741,9 +767,9 @@ int gemm_bf16_tn(const GemmArgs& a, int num_sms, cudaStream_t stream) {
         block_n = forced > 0 ? forced : choose_bn(a.M, a.N, num_sms);
     }
     // block_n < 0 selects the CTA-pair kernel with tile width -block_n (explicit: tests and tuning)
-    const bool pair = block_n < 0 && plain && a.epi != EPI_RELU2 && a.epi != EPI_GELU_TANH;
+    const bool pair = block_n < 0 && plain && a.epi != EPI_RELU2 && a.epi != EPI_GELU_TANH && a.epi != EPI_CLAMP_GLU;
     if (block_n < 0) block_n = -block_n;
-    if (block_n < 32 || block_n > 256 || (block_n % 16) || (a.epi == EPI_SWIGLU && (block_n % 32))) return -6;
+    if (block_n < 32 || block_n > 256 || (block_n % 16) || ((a.epi == EPI_SWIGLU || a.epi == EPI_CLAMP_GLU) && (block_n % 32))) return -6;
     if (pair) return (block_n % 32) ? -6 : launch_epi2(a, block_n, num_sms, stream);
     if (a.c_f32) {   // the fp32 tile store of the split-K instantiation, as one split
         GemmArgs p = a;

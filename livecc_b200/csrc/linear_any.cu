@@ -2,6 +2,7 @@
 // Two CUDA-core kernels cover every shape the tensor-core GEMM (gemm_tcgen05.cu) does not take: ragged N or K, fp32
 // storage (true fp32 FMAs, no reduced-precision matrix mode), and the few-row case of a decode step, where the
 // weight matrix is streamed once and every row of A is multiplied against it (HBM-bound).
+#include <type_traits>
 #include "common.cuh"
 #include "launch.h"
 #include "seqmix.h"
@@ -26,6 +27,9 @@ struct Grp {
     const int* a_rows;
     int act;
     int compact;   // few-row kernel with lists: blockIdx.y counts the non-empty lists of `compact` groups (0: blockIdx.y is the group)
+    int glu_F;     // few-row kernel, GLU form: a warp owns output column n = the gate row and the up row of that column
+    int glu_il16;
+    float glu_limit;
 };
 __device__ __forceinline__ float act_of(float v, int act) {
     if (act == ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
@@ -109,12 +113,12 @@ template <> struct Vec16<float> {
     }
 };
 
-template <typename T, typename TC, bool VEC, int WR>
+template <typename T, typename TC, bool VEC, int WR, bool GLU = false>
 __global__ void __launch_bounds__(256) linear_rows_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int ldw,
                                                           const float* __restrict__ bias, TC* __restrict__ C, int ldc, int M_all,
                                                           int N, int K, Grp g) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = (blockIdx.x * (blockDim.x >> 5) + warp) * WR;
+    const int n0 = (blockIdx.x * (blockDim.x >> 5) + warp) * (GLU ? 1 : WR);
     if (n0 >= N) return;
     int row0 = 0, z = blockIdx.y;
     if (g.row_off) {
@@ -146,11 +150,17 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const T* __restrict__ 
     for (int r = 0; r < WR; ++r)
 #pragma unroll
         for (int m = 0; m < kRowsMax; ++m) acc[r][m] = 0.f;
+    // the weight row behind accumulator r: output columns n0, n0 + 1, ...; in the GLU form (WR = 2) the gate row (r = 0) and
+    // the up row (r = 1) of output column n0
+    auto wrow = [&](int r) -> int {
+        if (GLU) return g.glu_il16 ? ((n0 >> 4) << 5) + (n0 & 15) + 16 * r : n0 + r * g.glu_F;
+        return min(n0 + r, N - 1);
+    };
     if (VEC) {
         constexpr int V = Vec16<T>::N;
         const T* w[WR];
 #pragma unroll
-        for (int r = 0; r < WR; ++r) w[r] = W + (size_t)min(n0 + r, N - 1) * ldw;
+        for (int r = 0; r < WR; ++r) w[r] = W + (size_t)wrow(r) * ldw;
         for (int kb = lane * V; kb < K; kb += 32 * V * WU) {
             uint4 wq[WR][WU];
 #pragma unroll
@@ -183,12 +193,23 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const T* __restrict__ 
         for (int k = lane; k < K; k += 32) {
 #pragma unroll
             for (int r = 0; r < WR; ++r) {
-                const float wv = ldf(W + (size_t)min(n0 + r, N - 1) * ldw + k);
+                const float wv = ldf(W + (size_t)wrow(r) * ldw + k);
 #pragma unroll
                 for (int m = 0; m < kRowsMax; ++m)
                     if (m < M) acc[r][m] = fmaf(ldf(arp[m] + k), wv, acc[r][m]);
             }
         }
+    }
+    if (GLU) {
+#pragma unroll
+        for (int m = 0; m < kRowsMax; ++m) {
+            if (m < M) {
+                const float gt = fminf(warp_sum(acc[0][m]), g.glu_limit);
+                const float up = fminf(fmaxf(warp_sum(acc[WR - 1][m]), -g.glu_limit), g.glu_limit);
+                if (lane == 0) stf(C + (size_t)m * ldc + n0, gt / (1.f + expf(-1.702f * gt)) * (up + 1.f));
+            }
+        }
+        continue;
     }
 #pragma unroll
     for (int r = 0; r < WR; ++r) {
@@ -206,7 +227,9 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const T* __restrict__ 
 
 template <typename T, typename TC>
 int launch_linear(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N, int K,
-                  cudaStream_t s, int groups = 1, Grp g = Grp{0, 0, 0, nullptr, nullptr, ACT_NONE, 0}, int M_total = 0) {
+                  cudaStream_t s, int groups = 1, Grp g = Grp{0, 0, 0, nullptr, nullptr, ACT_NONE, 0, 0, 0, 0.f}, int M_total = 0,
+                  void* glu_tmp = nullptr, int ld_tmp = 0) {
+    // GLU form: N = glu_F output columns from 2 * glu_F weight rows
     // lists: the row kernel while all groups together have few rows (a decode step routes `top` rows per sequence)
     if (g.row_off ? M_total <= 8 * kRowsMax : M <= kRowsMax) {
         constexpr int V = Vec16<T>::N;
@@ -215,6 +238,15 @@ int launch_linear(const void* A, int lda, const void* W, int ldw, const float* b
         int grid_y = groups;
         if (g.row_off && M_total < groups) { g.compact = groups; grid_y = M_total; }
         count_launch();
+        if (g.glu_F > 0) {
+            if constexpr (std::is_same<T, TC>::value) {
+                if (vec) linear_rows_kernel<T, TC, true, 2, true><<<dim3((N + 1) / 2, grid_y), 64, 0, s>>>((const T*)A, lda, (const T*)W, ldw, bias, (TC*)C, ldc, M, N, K, g);
+                else linear_rows_kernel<T, TC, false, 2, true><<<dim3((N + 1) / 2, grid_y), 64, 0, s>>>((const T*)A, lda, (const T*)W, ldw, bias, (TC*)C, ldc, M, N, K, g);
+                return cudaGetLastError() == cudaSuccess ? 0 : -100;
+            } else {
+                return -2;
+            }
+        }
 #define LCC_ROWS(VECB, WRN, WARPS)                                                                                         \
     linear_rows_kernel<T, TC, VECB, WRN><<<dim3((N + WARPS * WRN - 1) / (WARPS * WRN), grid_y), WARPS * 32, 0, s>>>(            \
         (const T*)A, lda, (const T*)W, ldw, bias, (TC*)C, ldc, M, N, K, g)
@@ -224,6 +256,18 @@ int launch_linear(const void* A, int lda, const void* W, int ldw, const float* b
             if (vec) LCC_ROWS(true, 1, 2); else LCC_ROWS(false, 1, 2);
         }
 #undef LCC_ROWS
+    } else if (g.glu_F > 0) {
+        // raw gate and up columns into the caller's scratch, then the activation as a row kernel
+        if (!glu_tmp || ld_tmp < 2 * N || !std::is_same<T, TC>::value) return -2;
+        Grp raw = g;
+        raw.glu_F = 0;
+        raw.c_stride = 0;
+        dim3 grid((2 * N + BN - 1) / BN, (M + BM - 1) / BM, groups);
+        count_launch();
+        linear_tile_kernel<T, T><<<grid, 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, bias, (T*)glu_tmp, ld_tmp, M, 2 * N, K, raw);
+        if (cudaGetLastError() != cudaSuccess) return -100;
+        const int rows = g.row_off ? M_total : M;
+        return glu_clamp_swish(sizeof(T) == 4 ? DT_F32 : DT_BF16, glu_tmp, ld_tmp, C, ldc, rows, N, g.glu_limit, s, g.glu_il16 != 0);
     } else {
         dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, groups);
         count_launch();
@@ -246,11 +290,14 @@ int linear_grouped(const GroupedLinear& q, cudaStream_t s) {
     if (!q.A || !q.W || !q.C || q.groups < 1 || q.groups > 65535 || q.M < 1 || q.N < 1 || q.K < 1 || q.lda < q.K || q.ldw < q.K ||
         q.ldc < q.N || (q.a_rows && !q.row_off))
         return -2;
-    const Grp g{q.a_stride, q.w_stride, q.c_stride, q.row_off, q.a_rows, q.act, 0};
+    if (q.glu_F > 0 && (q.N != q.glu_F || q.act != ACT_NONE || q.c_f32 || (q.glu_il16 && (q.glu_F % 16)) || q.c_stride != 0 ||
+                        (q.groups > 1 && !q.row_off)))
+        return -2;
+    const Grp g{q.a_stride, q.w_stride, q.c_stride, q.row_off, q.a_rows, q.act, 0, q.glu_F, q.glu_il16 ? 1 : 0, q.glu_limit};
     const int mt = q.row_off ? (q.M_total > 0 ? q.M_total : q.M * q.groups) : 0;
-    if (q.dt == DT_F32) return launch_linear<float, float>(q.A, q.lda, q.W, q.ldw, nullptr, q.C, q.ldc, q.M, q.N, q.K, s, q.groups, g, mt);
+    if (q.dt == DT_F32) return launch_linear<float, float>(q.A, q.lda, q.W, q.ldw, nullptr, q.C, q.ldc, q.M, q.N, q.K, s, q.groups, g, mt, q.glu_tmp, q.ld_tmp);
     if (q.c_f32) return launch_linear<bf16, float>(q.A, q.lda, q.W, q.ldw, nullptr, q.C, q.ldc, q.M, q.N, q.K, s, q.groups, g, mt);
-    return launch_linear<bf16, bf16>(q.A, q.lda, q.W, q.ldw, nullptr, q.C, q.ldc, q.M, q.N, q.K, s, q.groups, g, mt);
+    return launch_linear<bf16, bf16>(q.A, q.lda, q.W, q.ldw, nullptr, q.C, q.ldc, q.M, q.N, q.K, s, q.groups, g, mt, q.glu_tmp, q.ld_tmp);
 }
 
 }  // namespace lcc

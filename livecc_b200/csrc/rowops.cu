@@ -233,34 +233,87 @@ __global__ void __launch_bounds__(256) gather_norm_kernel(const float* __restric
     for (int c = threadIdx.x; c < W; c += blockDim.x) stf(out + (size_t)i * W + c, norm_apply(n, x[c], rn, c));
 }
 
+template <typename T> __device__ __forceinline__ void ld4(const T* p, float (&v)[4]);
+template <> __device__ __forceinline__ void ld4<float>(const float* p, float (&v)[4]) {
+    const float4 u = *reinterpret_cast<const float4*>(p);
+    v[0] = u.x; v[1] = u.y; v[2] = u.z; v[3] = u.w;
+}
+template <> __device__ __forceinline__ void ld4<bf16>(const bf16* p, float (&v)[4]) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <typename T> __device__ __forceinline__ void st4(T* p, const float (&v)[4]);
+template <> __device__ __forceinline__ void st4<float>(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <> __device__ __forceinline__ void st4<bf16>(bf16* p, const float (&v)[4]) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
+}
+
 // One CTA per row: pass 1 forms the new residual row (every addend read, also a row of xa that pass 2 rewrites) and, for a
-// norm with a row statistic, its sum of squares; pass 2 writes the normed row. A row's sums do not depend on S.
-template <typename T>
+// norm with a row statistic, its sum of squares; pass 2 writes the normed row. The places and weights of a routed row's
+// choices are read once into shared memory, so that the expert rows' loads do not wait on them one by one. VEC: four
+// columns per thread and step (every row start 16-byte aligned in fp32, 8-byte in bf16). Each column's sum is formed in the
+// same order in both forms and does not depend on S.
+constexpr int kCombineTop = 32;
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) residual_norm_kernel(float* __restrict__ x32, const T* __restrict__ a, int ld_a,
                                                             const T* __restrict__ b, int ld_b, bool has_mc, MoeCombine mc, NormSpec n,
                                                             T* __restrict__ xa, int W) {
     __shared__ float red[32];
+    __shared__ int spos[kCombineTop];
+    __shared__ float swt[kCombineTop];
     const int r = blockIdx.x;
     float* x = x32 + (size_t)r * W;
     float ss = 0.f;
+    constexpr int V = VEC ? 4 : 1;
     if (a || b || has_mc) {
-        const float gs = (has_mc && mc.so) ? mc.gate[r] : 0.f;
-        for (int c = threadIdx.x; c < W; c += blockDim.x) {
-            float y = a ? ldf(a + (size_t)r * ld_a + c) : 0.f;
-            if (has_mc) {
-                float acc = 0.f;
-                for (int k = 0; k < mc.top; ++k) {
-                    const int p = mc.pos[(size_t)r * mc.top + k];
-                    if (p >= 0) acc = fmaf(mc.weight[(size_t)r * mc.top + k], ldf((const T*)mc.eo + (size_t)p * mc.ld_eo + c), acc);
-                }
-                if (mc.so) acc = fmaf(gs, ldf((const T*)mc.so + (size_t)r * mc.ld_so + c), acc);
-                y += acc;
-            } else if (b) {
-                y += ldf(b + (size_t)r * ld_b + c);
+        const int top = has_mc ? mc.top : 0;
+        const bool cached = top <= kCombineTop;
+        if (has_mc && cached) {
+            if (threadIdx.x < top) {
+                spos[threadIdx.x] = mc.pos[(size_t)r * top + threadIdx.x];
+                swt[threadIdx.x] = mc.weight[(size_t)r * top + threadIdx.x];
             }
-            const float v = x[c] + y;
-            x[c] = v;
-            ss = fmaf(v, v, ss);
+            __syncthreads();
+        }
+        const float gs = (has_mc && mc.so) ? mc.gate[r] : 0.f;
+        for (int c = threadIdx.x * V; c < W; c += blockDim.x * V) {
+            float y[V], t[V];
+#pragma unroll
+            for (int i = 0; i < V; ++i) y[i] = 0.f;
+            if (has_mc) {
+                for (int k = 0; k < top; ++k) {
+                    const int p = cached ? spos[k] : mc.pos[(size_t)r * top + k];
+                    if (p < 0) continue;
+                    const float wk = cached ? swt[k] : mc.weight[(size_t)r * top + k];
+                    const T* src = (const T*)mc.eo + (size_t)p * mc.ld_eo + c;
+                    if (VEC) ld4(src, (float(&)[4])t); else t[0] = ldf(src);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) y[i] = fmaf(wk, t[i], y[i]);
+                }
+                if (mc.so) {
+                    const T* src = (const T*)mc.so + (size_t)r * mc.ld_so + c;
+                    if (VEC) ld4(src, (float(&)[4])t); else t[0] = ldf(src);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) y[i] = fmaf(gs, t[i], y[i]);
+                }
+            } else if (b) {
+                const T* src = b + (size_t)r * ld_b + c;
+                if (VEC) ld4(src, (float(&)[4])y); else y[0] = ldf(src);
+            }
+            if (a) {
+                const T* src = a + (size_t)r * ld_a + c;
+                if (VEC) ld4(src, (float(&)[4])t); else t[0] = ldf(src);
+#pragma unroll
+                for (int i = 0; i < V; ++i) y[i] += t[i];       // the mixer's row + the feed-forward's row
+            }
+            float v[V];
+            if (VEC) ld4(x + c, (float(&)[4])v); else v[0] = x[c];
+#pragma unroll
+            for (int i = 0; i < V; ++i) { v[i] += y[i]; ss = fmaf(v[i], v[i], ss); }
+            if (VEC) st4(x + c, (const float(&)[4])v); else x[c] = v[0];
         }
     } else if (n.w && n.kind == NORM_RMS) {
         for (int c = threadIdx.x; c < W; c += blockDim.x) ss = fmaf(x[c], x[c], ss);
@@ -270,19 +323,25 @@ __global__ void __launch_bounds__(256) residual_norm_kernel(float* __restrict__ 
     if (n.kind == NORM_RMS) {
         ss = block_sum(ss, red);
         rn = 1.f / sqrtf(ss / (float)W + n.eps);
-    } else {
-        __syncthreads();       // every read of the old xa row (identity experts) is done before it is rewritten
     }
-    for (int c = threadIdx.x; c < W; c += blockDim.x) stf(xa + (size_t)r * W + c, norm_apply(n, x[c], rn, c));
+    // (a thread rewrites in xa only the columns it read in pass 1: an xa row that served as an addend is safe)
+    for (int c = threadIdx.x * V; c < W; c += blockDim.x * V) {
+        float v[V];
+        if (VEC) ld4(x + c, (float(&)[4])v); else v[0] = x[c];
+#pragma unroll
+        for (int i = 0; i < V; ++i) v[i] = norm_apply(n, v[i], rn, c + i);
+        if (VEC) st4(xa + (size_t)r * W + c, (const float(&)[4])v); else stf(xa + (size_t)r * W + c, v[0]);
+    }
 }
 
 template <typename T>
-__global__ void glu_clamp_swish_kernel(const T* __restrict__ gu, int ld, T* __restrict__ out, int ld_out, int S, int F, float limit) {
+__global__ void glu_clamp_swish_kernel(const T* __restrict__ gu, int ld, T* __restrict__ out, int ld_out, int S, int F, float limit, bool il16) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (int64_t)S * F) return;
     const int r = (int)(i / F), c = (int)(i % F);
-    const float g = fminf(ldf(gu + (size_t)r * ld + c), limit);
-    const float u = fminf(fmaxf(ldf(gu + (size_t)r * ld + F + c), -limit), limit);
+    const int gc = il16 ? ((c >> 4) << 5) + (c & 15) : c, uc = il16 ? gc + 16 : F + c;
+    const float g = fminf(ldf(gu + (size_t)r * ld + gc), limit);
+    const float u = fminf(fmaxf(ldf(gu + (size_t)r * ld + uc), -limit), limit);
     stf(out + (size_t)r * ld_out + c, g / (1.f + expf(-1.702f * g)) * (u + 1.f));
 }
 
@@ -402,21 +461,26 @@ int residual_norm(int dt, float* x32, const void* a, int ld_a, const void* b, in
     if (!a && !b && !mc && !next.w) return 0;
     count_launch();
     const MoeCombine m = mc ? *mc : MoeCombine{};
-    if (dt == DT_F32)
-        residual_norm_kernel<float><<<S, 256, 0, s>>>(x32, (const float*)a, ld_a, (const float*)b, ld_b, mc != nullptr, m, next, (float*)xa, W);
-    else
-        residual_norm_kernel<bf16><<<S, 256, 0, s>>>(x32, (const bf16*)a, ld_a, (const bf16*)b, ld_b, mc != nullptr, m, next, (bf16*)xa, W);
+    const size_t es = dt == DT_F32 ? 4 : 2;
+    auto ok4 = [&](const void* p, int ld) { return !p || ((ld % 4) == 0 && ((uintptr_t)p % (4 * es)) == 0); };
+    const bool vec = (W % 4) == 0 && ((uintptr_t)x32 % 16) == 0 && ok4(a, ld_a) && ok4(b, ld_b) && ok4(xa, W) &&
+                     (!mc || (ok4(m.eo, m.ld_eo) && ok4(m.so, m.ld_so)));
+#define LCC_RN(T, VECB)                                                                                                      \
+    residual_norm_kernel<T, VECB><<<S, 256, 0, s>>>(x32, (const T*)a, ld_a, (const T*)b, ld_b, mc != nullptr, m, next, (T*)xa, W)
+    if (dt == DT_F32) { if (vec) LCC_RN(float, true); else LCC_RN(float, false); }
+    else { if (vec) LCC_RN(bf16, true); else LCC_RN(bf16, false); }
+#undef LCC_RN
     return done();
 }
 
-int glu_clamp_swish(int dt, const void* gu, int ld, void* out, int ld_out, int S, int F, float limit, cudaStream_t s) {
-    if (!gu || !out || S < 1 || F < 1) return -2;
+int glu_clamp_swish(int dt, const void* gu, int ld, void* out, int ld_out, int S, int F, float limit, cudaStream_t s, bool il16) {
+    if (!gu || !out || S < 1 || F < 1 || (il16 && (F % 16))) return -2;
     const int64_t n = (int64_t)S * F;
     count_launch();
     if (dt == DT_F32)
-        glu_clamp_swish_kernel<float><<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const float*)gu, ld, (float*)out, ld_out, S, F, limit);
+        glu_clamp_swish_kernel<float><<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const float*)gu, ld, (float*)out, ld_out, S, F, limit, il16);
     else
-        glu_clamp_swish_kernel<bf16><<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const bf16*)gu, ld, (bf16*)out, ld_out, S, F, limit);
+        glu_clamp_swish_kernel<bf16><<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const bf16*)gu, ld, (bf16*)out, ld_out, S, F, limit, il16);
     return done();
 }
 

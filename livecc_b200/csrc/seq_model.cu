@@ -259,6 +259,7 @@ lcc_seq_model* lcc_seq_model_create(lcc_ctx* ctx, const lcc_seq_model_desc* desc
                 return fail("routed feed-forward: the kept groups must be equal groups that hold at least `top` experts");
             if (l.e_router_kind != LCC_ROUTER_SIGMOID && l.e_router_kind != LCC_ROUTER_SOFTMAX) return fail("unknown router kind");
             if (l.e_act != LCC_EXPERT_RELU2 && l.e_act != LCC_EXPERT_CLAMP_GLU) return fail("unknown expert activation");
+            if (l.e_up_il16 && (l.e_act != LCC_EXPERT_CLAMP_GLU || l.e_ff % 16)) return fail("interleaved gate / up rows need a gated expert width that is a multiple of 16");
         } else if (l.ff_kind != LCC_FF_GLU && l.ff_kind != LCC_FF_MLP) {
             return fail("unknown feed-forward kind");
         }
@@ -655,21 +656,26 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
             if (tc) {
                 STEP(lcc::moe_gather_rows(dt, xa, W, src_row, ex, ldw8, n_tiles * kMoeTile, W, s), "expert row gather");
                 lcc::GemmArgs a;
-                a.A = ex; a.B = l.e_up; a.C = eh; a.M = n_tiles * kMoeTile; a.N = NH; a.K = W; a.lda = ldw8; a.ldb = W; a.ldc = ldh;
-                a.bias = nullptr; a.residual = nullptr; a.ldr = 0; a.epi = glu ? lcc::EPI_NONE : lcc::EPI_RELU2; a.block_n = 0;
+                // gated experts with interleaved rows: the activation is the up product's epilogue and the hidden rows land in eg
+                const bool epi_glu = glu && l.e_up_il16;
+                a.A = ex; a.B = l.e_up; a.C = epi_glu ? eg : eh; a.M = n_tiles * kMoeTile; a.N = NH; a.K = W; a.lda = ldw8; a.ldb = W;
+                a.ldc = epi_glu ? ldg : ldh;
+                a.bias = nullptr; a.residual = nullptr; a.ldr = 0; a.block_n = 0;
+                a.epi = epi_glu ? lcc::EPI_CLAMP_GLU : (glu ? lcc::EPI_NONE : lcc::EPI_RELU2); a.epi_param = l.e_limit;
                 a.tile_group = tile_group; a.groups = E;
                 STEP(lcc::gemm_bf16_tn(a, m->ctx->num_sms, s), "experts up");
-                if (glu) STEP(lcc::glu_clamp_swish(dt, eh, ldh, eg, ldg, n_tiles * kMoeTile, l.e_ff, l.e_limit, s), "expert activation");
+                if (glu && !epi_glu) STEP(lcc::glu_clamp_swish(dt, eh, ldh, eg, ldg, n_tiles * kMoeTile, l.e_ff, l.e_limit, s), "expert activation");
                 a.A = glu ? eg : eh; a.B = l.e_down; a.C = eo; a.N = W; a.K = l.e_ff; a.lda = glu ? ldg : ldh; a.ldb = l.e_ff; a.ldc = ldw8; a.epi = lcc::EPI_NONE;
                 STEP(lcc::gemm_bf16_tn(a, m->ctx->num_sms, s), "experts down");
             } else {
                 lcc::GroupedLinear g{};
                 g.dt = dt; g.A = xa; g.lda = W; g.a_stride = 0; g.a_rows = src_row; g.row_off = row_off; g.M_total = T * K;
                 g.W = l.e_up; g.ldw = W; g.w_stride = (int64_t)NH * W;
-                g.C = eh; g.ldc = ldh; g.c_stride = 0; g.c_f32 = false;
-                g.groups = E; g.M = T; g.N = NH; g.K = W; g.act = up_act;
+                g.C = glu ? eg : eh; g.ldc = glu ? ldg : ldh; g.c_stride = 0; g.c_f32 = false;
+                g.groups = E; g.M = T; g.N = l.e_ff; g.K = W; g.act = up_act;
+                if (glu) { g.glu_F = l.e_ff; g.glu_il16 = l.e_up_il16 != 0; g.glu_limit = l.e_limit; g.glu_tmp = eh; g.ld_tmp = ldh; }
                 STEP(lcc::linear_grouped(g, s), "experts up");
-                if (glu) STEP(lcc::glu_clamp_swish(dt, eh, ldh, eg, ldg, T * K, l.e_ff, l.e_limit, s), "expert activation");
+                g.glu_F = 0; g.glu_tmp = nullptr;
                 g.A = glu ? eg : eh; g.lda = glu ? ldg : ldh; g.a_rows = nullptr;
                 g.W = l.e_down; g.ldw = l.e_ff; g.w_stride = (int64_t)W * l.e_ff;
                 g.C = eo; g.ldc = ldw8; g.N = W; g.K = l.e_ff; g.act = lcc::ACT_NONE;

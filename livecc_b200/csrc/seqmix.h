@@ -54,6 +54,12 @@ struct GroupedLinear {
     int groups, M, N, K;
     const int* row_off; const int* a_rows; int M_total;
     int act;
+    // Gated experts (glu_F > 0): W holds 2 * glu_F rows per group, gate and up rows either [gate: F | up: F] or, with glu_il16,
+    // interleaved in groups of 16 (16 gate rows, then the 16 matching up rows); N = glu_F and C receives
+    // g * sigmoid(1.702 g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit). The few-row kernel forms it in its
+    // store; the tile kernel writes the 2 * glu_F raw columns to glu_tmp (leading dimension ld_tmp, storage dt, the rows of C)
+    // and a row kernel follows.
+    int glu_F; bool glu_il16; float glu_limit; void* glu_tmp; int ld_tmp;
 };
 enum { ACT_NONE = 0, ACT_RELU2 = 1, ACT_GELU_TANH = 2 };   // 2: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))
 int linear_grouped(const GroupedLinear& g, cudaStream_t s);
@@ -247,8 +253,9 @@ int gather_norm(int dt, const float* x32, const int* rows, const NormSpec& n, vo
 // mc->so may be xa itself (identity experts return the block's normed input): every element is read before it is rewritten.
 int residual_norm(int dt, float* x32, const void* a, int ld_a, const void* b, int ld_b, const MoeCombine* mc, const NormSpec& next,
                   void* xa, int S, int W, cudaStream_t s);
-// out[r, c] = g * sigmoid(1.702 g) * (u + 1), g = min(gu[r, c], limit), u = clamp(gu[r, F + c], -limit, limit)
-int glu_clamp_swish(int dt, const void* gu, int ld, void* out, int ld_out, int S, int F, float limit, cudaStream_t s);
+// out[r, c] = g * sigmoid(1.702 g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit); gate = gu[r, c] and
+// up = gu[r, F + c], or with il16 (columns interleaved in groups of 16) gate = gu[r, (c / 16) * 32 + c % 16], up 16 further
+int glu_clamp_swish(int dt, const void* gu, int ld, void* out, int ld_out, int S, int F, float limit, cudaStream_t s, bool il16 = false);
 // x <- cap * tanh(x / cap) in place (fp32; cap <= 0: unchanged), then x <- x * scale
 int softcap(float* x, int64_t n, float cap, cudaStream_t s, float scale = 1.f);
 

@@ -66,6 +66,22 @@ def kedelorn_config(width: int, n_layers: int, ff: int, vocab: int = 32768) -> S
                                      "norm": {"eps": 1e-6}})
 
 
+def dibedra_config(width: int, n_layers: int, ff: int, window: int, vocab: int = 32768) -> SeqModelConfig:
+    """Parallel blocks; every layer sliding-window attention with 128-channel heads (8 query heads per key/value head, the
+    first 64 channels rotated, long-context frequencies). The first layer has a two-matrix feed-forward of width 3 ff / 2,
+    every other layer 16 experts of width ff/4 and 2 identity experts, 4 per token out of the best 6 of 9 groups: a token
+    whose four choices are real experts reads 3 x width x ff feed-forward weights, the dense gated `ff` of the models beside it."""
+    heads, layers = width // 128, []
+    rot = {"dims": 64, "base": 250000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    mx = dict(heads=heads, kv_heads=max(1, heads // 8), dim=128, vdim=128, mask={"size": window}, rot=rot, scale=128 ** -0.5)
+    moe = {"kind": "moe", "expert": {"ff": ff // 4 // 8 * 8, "limit": 7.0},
+           "router": {"experts": 16, "identity": 2, "top": 4, "groups": {"count": 9, "keep": 6}}}
+    for i in range(n_layers):
+        layers.append({"type": "attention", "mixer": mx, "mlp": {"kind": "dense", "ff": 3 * ff // 2 // 8 * 8} if i == 0 else moe})
+    return SeqModelConfig.from_json({"architecture": "Dibedra", "vocab": vocab, "width": width, "layers": layers, "norm": {"eps": 1e-6},
+                                     "logit_scale": 0.5})
+
+
 def qwen_config(width: int, n_layers: int, ff: int, vocab: int = 32768) -> LiveCCConfig:
     heads = width // 128
     return LiveCCConfig(
@@ -133,8 +149,10 @@ def run(sizes: List[str], prompt_lens: List[int], new_tokens: int, steps: int, w
     for name in sizes:
         width, n_layers, ff, chunk = SIZES[name]
         rec = {}
-        for label, cfg in ([("kedelorn", kedelorn_config(width, n_layers, ff))] if design == "Kedelorn" else []) + \
-                [("bimopel", seq_config(width, n_layers, ff, chunk))]:
+        arms = {"Bimopel": ["bimopel"], "Kedelorn": ["kedelorn", "bimopel"], "Dibedra": ["dibedra", "kedelorn"]}[design]
+        make = {"bimopel": lambda: seq_config(width, n_layers, ff, chunk), "kedelorn": lambda: kedelorn_config(width, n_layers, ff),
+                "dibedra": lambda: dibedra_config(width, n_layers, ff, chunk)}
+        for label, cfg in [(a, make[a]()) for a in arms]:
             m = SeqLMForCausalLM.from_state_dict(cfg, synthetic_seq_tensors(cfg, seed=7, device="cuda"), dtype,
                                                  max_tokens=max(prompt_lens) + new_tokens + 64)
             rec["weights_gb" if label == "bimopel" else label + "_weights_gb"] = round(m.weights.nbytes() / 1e9, 3)
@@ -156,7 +174,7 @@ def run(sizes: List[str], prompt_lens: List[int], new_tokens: int, steps: int, w
 
 
 def main(args, design: str = "Bimopel") -> Dict:
-    """bench.py --arch seq | kedelorn: one JSON line; `value` = decode tokens/s of the first size at the first prompt length."""
+    """bench.py --arch seq | kedelorn | dibedra: one JSON line; `value` = decode tokens/s of the first size at the first prompt length."""
     sizes = [s for s in (args.seq_sizes.split(",") if args.seq_sizes else list(SIZES)) if s in SIZES]
     lens = [int(x) for x in args.seq_prompt.split(",")]
     res = run(sizes, lens, args.max_new_tokens if args.max_new_tokens > 16 else 64, args.steps, max(args.warmup, 3), design=design)
@@ -164,7 +182,7 @@ def main(args, design: str = "Bimopel") -> Dict:
     return {"metric": "decode_tokens_per_s", "value": first["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": first["decode_ms_per_token"], "higher_is_better": True, "dtype": "bf16",
             "data": "synthetic (random weights, random ids)", "vs_baseline": None,
-            "config": {"model": f"{design} {sizes[0]} beside " + ("Bimopel and the " if design == "Kedelorn" else "") +
+            "config": {"model": f"{design} {sizes[0]} beside " + {"Kedelorn": "Bimopel and the ", "Dibedra": "Kedelorn and the "}.get(design, "") +
                                 "Qwen2-style decoder of equal width/depth/ff", "global_batch": 1,
                        "seq_len": lens[0], "parallelism": "1 gpu", "l2": "weights of every size exceed L2"},
             "sizes": res}

@@ -206,11 +206,21 @@ class SeqWeights:
                 for j in range(e.experts):
                     check(f"{m}e{j}.up", (e.ff, W)), check(f"{m}e{j}.down", (W, e.ff))
                 check(m + "router", (e.outputs, W)), check(m + "correction", (e.outputs,))
-                if e.act == "clamp_glu":     # each expert's gate rows, then its up rows: one product per expert list
+                if e.act == "clamp_glu":
+                    # each expert's gate and up rows in one matrix, so that one product per expert list yields both. Widths that
+                    # are multiples of 16 interleave them in groups of 16 rows (the layout whose activation the tensor-core
+                    # product's epilogue forms from neighbouring accumulator columns); other widths keep [gate | up].
                     for j in range(e.experts):
                         check(f"{m}e{j}.gate", (e.ff, W))
-                    w["e_up"] = torch.stack([torch.cat([get(f"{m}e{j}.gate"), get(f"{m}e{j}.up")], 0) for j in range(e.experts)]) \
-                        .to(device=device, dtype=dtype).contiguous()
+                    w["e_up_il16"] = int(e.ff % 16 == 0)
+
+                    def gate_up(j):
+                        g, u = get(f"{m}e{j}.gate"), get(f"{m}e{j}.up")
+                        if not w["e_up_il16"]:
+                            return torch.cat([g, u], 0)
+                        return torch.stack([g.view(e.ff // 16, 16, W), u.view(e.ff // 16, 16, W)], 1).reshape(2 * e.ff, W)
+
+                    w["e_up"] = torch.stack([gate_up(j) for j in range(e.experts)]).to(device=device, dtype=dtype).contiguous()
                 else:
                     w["e_up"] = torch.stack([get(f"{m}e{j}.up") for j in range(e.experts)]).to(device=device, dtype=dtype).contiguous()
                 w["e_down"] = torch.stack([get(f"{m}e{j}.down") for j in range(e.experts)]).to(device=device, dtype=dtype).contiguous()
@@ -341,6 +351,7 @@ class SeqLMForCausalLM:
                 e.e_router_kind = _cabi.ROUTER_SOFTMAX if x.router == "softmax" else _cabi.ROUTER_SIGMOID
                 e.e_identity, e.e_groups, e.e_keep, e.e_limit = x.identity, x.groups, x.keep, x.limit
                 e.e_act = _cabi.EXPERT_CLAMP_GLU if x.act == "clamp_glu" else _cabi.EXPERT_RELU2
+                e.e_up_il16 = lw.get("e_up_il16", 0)
                 e.norm2_f32, e.e_router, e.e_correction_f32 = p(lw.get("norm2")), p(lw["e_router"]), p(lw["e_correction"])
                 e.e_up, e.e_down = p(lw["e_up"]), p(lw["e_down"])
                 e.e_shared_up, e.e_shared_down = p(lw.get("e_shared_up")), p(lw.get("e_shared_down"))

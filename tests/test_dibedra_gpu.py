@@ -468,8 +468,11 @@ def test_generation_moves_the_window_across_pages_under_graph_replay():
     out.past_key_values.release()
 
 
-def test_trace_replay_command_line(tmp_path):
-    d = K.CASES["looped"]
+@pytest.mark.parametrize("dtype,name", [("float32", "looped"), ("bfloat16", "dense")])
+def test_trace_replay_command_line(tmp_path, dtype, name):
+    """(bf16 storage on the stack without routers: with only four rows compared, one router choice that falls the other way
+    under rounding would decide the result.)"""
+    d = K.CASES[name]
     tensors = synthetic_seq_tensors(SeqModelConfig.from_json(d), seed=21)
     mdir = tmp_path / "model"
     mdir.mkdir()
@@ -481,18 +484,17 @@ def test_trace_replay_command_line(tmp_path):
              {"step": 2, "entries": [{"id": "x", "tokens": a[35:], "want": [14]}], "end": ["x"]},
              {"step": 3, "entries": [{"id": "y", "tokens": b, "want": [6]}], "end": ["y"]}]
     out = tmp_path / "out"
-    for dtype in ("float32", "bfloat16"):
-        r = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", str(mdir), "--dtype", dtype, "--out", str(out),
-                            "--max-tokens", "64"], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True,
-                           timeout=600)
-        assert r.returncode == 0, r.stderr[-2000:]
-        assert [l for l in r.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(4)]
-        assert not (out / "1.f32").exists()
-        import numpy as np
+    r = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", str(mdir), "--dtype", dtype, "--out", str(out),
+                        "--max-tokens", "64"], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True,
+                       timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(4)]
+    assert not (out / "1.f32").exists()
+    import numpy as np
 
-        la, lb = O.forward(d, tensors, a), O.forward(d, tensors, b)
-        g0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4")).reshape(2, -1)
-        g2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4")).reshape(1, -1)
-        g3 = torch.from_numpy(np.fromfile(out / "3.f32", dtype="<f4")).reshape(1, -1)
-        got, want = torch.cat([g0, g2, g3]), torch.cat([la[[0, 32]], la[[49]], lb[[6]]])
-        assert rel(got, want) < (F32_TOL if dtype == "float32" else BF16_TOL)
+    la, lb = O.forward(d, tensors, a), O.forward(d, tensors, b)
+    g0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4")).reshape(2, -1)
+    g2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4")).reshape(1, -1)
+    g3 = torch.from_numpy(np.fromfile(out / "3.f32", dtype="<f4")).reshape(1, -1)
+    got, want = torch.cat([g0, g2, g3]), torch.cat([la[[0, 32]], la[[49]], lb[[6]]])
+    assert rel(got, want) < (F32_TOL if dtype == "float32" else BF16_TOL)
