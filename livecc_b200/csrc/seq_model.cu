@@ -429,6 +429,13 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
     for (int li = 0; li < d.n_layers; ++li) {
         const lcc_seq_layer& l = m->layers[li];
         const Dims z = dims_of(l);
+        const bool has_ff = l.ff > 0 || l.ff_kind == LCC_FF_MOE;
+        // parallel block, few rows (every kernel latency-bound): the feed-forward depends on the normed row only and runs on
+        // the second stream beside the mixer (inside a capture: two branches of the graph), joined before the residual sum
+        const bool fork_ff = par && has_ff && m->side && T <= kForkMaxRows && (l.ff_kind == LCC_FF_MOE || l.ff_kind == LCC_FF_MLP);
+        if (fork_ff && (cudaEventRecord(m->ev_fork, s) != cudaSuccess || cudaStreamWaitEvent(m->side, m->ev_fork, 0) != cudaSuccess))
+            LCC_FAIL(m->ctx, -100, "stream fork failed");
+        cudaStream_t fs = fork_ff ? m->side : s;
         if (hc) STEP(boundary(l.hc1_f32, l.norm1_f32, (layer_dump && li > 0) ? layer_dump + (size_t)(li - 1) * T * W : nullptr), "stream boundary");
         if (l.type == LCC_MIX_RETENTION) {
             // [q | k | v | gate] -> rotary q, k (k scaled), everything that enters the recurrence packed as fp32 -> recurrence
@@ -610,7 +617,6 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
         else if (par) {}   // the feed-forward reads the same normed row; the residual sum closes the layer
         else if (l.type != LCC_MIX_PARALLEL)
             STEP(lcc::postnorm_residual(dt, x32, xa, o1, W, nullptr, nullptr, 0, nullptr, l.norm1_f32, d.alpha, d.eps, T, W, s), "norm1");
-        const bool has_ff = l.ff > 0 || l.ff_kind == LCC_FF_MOE;
         if (has_ff && hc) STEP(boundary(l.hc2_f32, l.norm2_f32, nullptr), "stream boundary");
         lcc::MoeCombine par_mc{};       // parallel block: the routed feed-forward's row is formed by the layer's residual kernel
         bool par_is_mc = false;
@@ -634,27 +640,27 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
             const int rows_max = T * K + E * (kMoeTile - 1), n_tiles = (rows_max + kMoeTile - 1) / kMoeTile;
             // the shared expert depends on the normed row only: in few-row steps, where every kernel is latency-bound, it runs on
             // the second stream beside the router and the routed experts
-            const bool fork = shared && m->side && T <= kForkMaxRows;
-            if (fork && (cudaEventRecord(m->ev_fork, s) != cudaSuccess || cudaStreamWaitEvent(m->side, m->ev_fork, 0) != cudaSuccess))
+            const bool fork = shared && m->side && T <= kForkMaxRows && !fork_ff;
+            if (fork && (cudaEventRecord(m->ev_fork, fs) != cudaSuccess || cudaStreamWaitEvent(m->side, m->ev_fork, 0) != cudaSuccess))
                 LCC_FAIL(m->ctx, -100, "stream fork failed");
             if (shared) {
-                cudaStream_t ss = fork ? m->side : s;
+                cudaStream_t ss = fork ? m->side : fs;
                 STEP(linear(m, xa, W, l.e_shared_up, nullptr, mid2, lds, false, T, l.e_shared_ff, W, ss, nullptr, lcc::ACT_RELU2), "shared expert up");
                 STEP(linear(m, mid2, lds, l.e_shared_down, nullptr, o2, W, false, T, W, l.e_shared_ff, ss), "shared expert down");
             }
             // router logits (and the shared expert's gate logit) accumulate in fp32 from the normed row
-            STEP(linear(m, xa, W, l.e_router, nullptr, logit, lde, true, T, EO + (shared ? 1 : 0), W, s), "router");
+            STEP(linear(m, xa, W, l.e_router, nullptr, logit, lde, true, T, EO + (shared ? 1 : 0), W, fs), "router");
             if (!tc && T * K <= 256 && EO <= 512) {
                 STEP(lcc::moe_route_small(logit, lde, l.e_correction_f32, EO, K, l.e_scale, sel, wsel, gate_out, row_off, posn,
-                                          src_row, T, s, &ro), "expert choice + row lists");
+                                          src_row, T, fs, &ro), "expert choice + row lists");
             } else {
-                if (cudaMemsetAsync(counts, 0, sizeof(int) * E, s) != cudaSuccess) LCC_FAIL(m->ctx, -100, "router counters");
-                if (tc && cudaMemsetAsync(src_row, 0xff, sizeof(int) * (size_t)n_tiles * kMoeTile, s) != cudaSuccess) LCC_FAIL(m->ctx, -100, "row lists");
-                STEP(lcc::moe_route(logit, lde, l.e_correction_f32, EO, K, l.e_scale, sel, wsel, gate_out, counts, rank, T, s, &ro), "expert choice");
-                STEP(lcc::moe_index(sel, rank, counts, E, K, tc ? kMoeTile : 1, row_off, posn, src_row, tc ? tile_group : nullptr, n_tiles, T, s), "expert row lists");
+                if (cudaMemsetAsync(counts, 0, sizeof(int) * E, fs) != cudaSuccess) LCC_FAIL(m->ctx, -100, "router counters");
+                if (tc && cudaMemsetAsync(src_row, 0xff, sizeof(int) * (size_t)n_tiles * kMoeTile, fs) != cudaSuccess) LCC_FAIL(m->ctx, -100, "row lists");
+                STEP(lcc::moe_route(logit, lde, l.e_correction_f32, EO, K, l.e_scale, sel, wsel, gate_out, counts, rank, T, fs, &ro), "expert choice");
+                STEP(lcc::moe_index(sel, rank, counts, E, K, tc ? kMoeTile : 1, row_off, posn, src_row, tc ? tile_group : nullptr, n_tiles, T, fs), "expert row lists");
             }
             if (tc) {
-                STEP(lcc::moe_gather_rows(dt, xa, W, src_row, ex, ldw8, n_tiles * kMoeTile, W, s), "expert row gather");
+                STEP(lcc::moe_gather_rows(dt, xa, W, src_row, ex, ldw8, n_tiles * kMoeTile, W, fs), "expert row gather");
                 lcc::GemmArgs a;
                 // gated experts with interleaved rows: the activation is the up product's epilogue and the hidden rows land in eg
                 const bool epi_glu = glu && l.e_up_il16;
@@ -663,10 +669,10 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
                 a.bias = nullptr; a.residual = nullptr; a.ldr = 0; a.block_n = 0;
                 a.epi = epi_glu ? lcc::EPI_CLAMP_GLU : (glu ? lcc::EPI_NONE : lcc::EPI_RELU2); a.epi_param = l.e_limit;
                 a.tile_group = tile_group; a.groups = E;
-                STEP(lcc::gemm_bf16_tn(a, m->ctx->num_sms, s), "experts up");
-                if (glu && !epi_glu) STEP(lcc::glu_clamp_swish(dt, eh, ldh, eg, ldg, n_tiles * kMoeTile, l.e_ff, l.e_limit, s), "expert activation");
+                STEP(lcc::gemm_bf16_tn(a, m->ctx->num_sms, fs), "experts up");
+                if (glu && !epi_glu) STEP(lcc::glu_clamp_swish(dt, eh, ldh, eg, ldg, n_tiles * kMoeTile, l.e_ff, l.e_limit, fs), "expert activation");
                 a.A = glu ? eg : eh; a.B = l.e_down; a.C = eo; a.N = W; a.K = l.e_ff; a.lda = glu ? ldg : ldh; a.ldb = l.e_ff; a.ldc = ldw8; a.epi = lcc::EPI_NONE;
-                STEP(lcc::gemm_bf16_tn(a, m->ctx->num_sms, s), "experts down");
+                STEP(lcc::gemm_bf16_tn(a, m->ctx->num_sms, fs), "experts down");
             } else {
                 lcc::GroupedLinear g{};
                 g.dt = dt; g.A = xa; g.lda = W; g.a_stride = 0; g.a_rows = src_row; g.row_off = row_off; g.M_total = T * K;
@@ -674,14 +680,14 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
                 g.C = glu ? eg : eh; g.ldc = glu ? ldg : ldh; g.c_stride = 0; g.c_f32 = false;
                 g.groups = E; g.M = T; g.N = l.e_ff; g.K = W; g.act = up_act;
                 if (glu) { g.glu_F = l.e_ff; g.glu_il16 = l.e_up_il16 != 0; g.glu_limit = l.e_limit; g.glu_tmp = eh; g.ld_tmp = ldh; }
-                STEP(lcc::linear_grouped(g, s), "experts up");
+                STEP(lcc::linear_grouped(g, fs), "experts up");
                 g.glu_F = 0; g.glu_tmp = nullptr;
                 g.A = glu ? eg : eh; g.lda = glu ? ldg : ldh; g.a_rows = nullptr;
                 g.W = l.e_down; g.ldw = l.e_ff; g.w_stride = (int64_t)W * l.e_ff;
                 g.C = eo; g.ldc = ldw8; g.N = W; g.K = l.e_ff; g.act = lcc::ACT_NONE;
-                STEP(lcc::linear_grouped(g, s), "experts down");
+                STEP(lcc::linear_grouped(g, fs), "experts down");
             }
-            if (fork && (cudaEventRecord(m->ev_join, m->side) != cudaSuccess || cudaStreamWaitEvent(s, m->ev_join, 0) != cudaSuccess))
+            if (fork && (cudaEventRecord(m->ev_join, m->side) != cudaSuccess || cudaStreamWaitEvent(fs, m->ev_join, 0) != cudaSuccess))
                 LCC_FAIL(m->ctx, -100, "stream join failed");
             if (hc) {   // the weighted sum of the experts' rows is formed by the boundary kernel that folds it into the streams
                 pend_mc = lcc::MoeCombine{eo, ldw8, posn, wsel, K, shared ? o2 : nullptr, W, sgate};
@@ -690,18 +696,21 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
                 par_mc = lcc::MoeCombine{eo, ldw8, posn, wsel, K, shared ? (const void*)o2 : (ident ? (const void*)xa : nullptr), W, sgate};
                 par_is_mc = true;
             } else {
-                STEP(lcc::moe_combine(dt, eo, ldw8, posn, wsel, K, shared ? o2 : nullptr, W, sgate, o1, W, T, W, s), "expert combine");
+                STEP(lcc::moe_combine(dt, eo, ldw8, posn, wsel, K, shared ? o2 : nullptr, W, sgate, o1, W, T, W, fs), "expert combine");
             }
         } else if (l.ff > 0 && l.ff_kind == LCC_FF_MLP) {
             const int ldf = ld8(l.ff);
-            STEP(linear(m, xa, W, l.ff_in, nullptr, mid, ldf, false, T, l.ff, W, s, nullptr, lcc::ACT_GELU_TANH), "feed-forward up + gelu");
-            STEP(linear(m, mid, ldf, l.ff_out, nullptr, par ? o2 : o1, W, false, T, W, l.ff, s), "feed-forward down");
+            // (its hidden rows in mid2: in a parallel block the mixer's rows in mid may still be in use on the other stream)
+            STEP(linear(m, xa, W, l.ff_in, nullptr, mid2, ldf, false, T, l.ff, W, fs, nullptr, lcc::ACT_GELU_TANH), "feed-forward up + gelu");
+            STEP(linear(m, mid2, ldf, l.ff_out, nullptr, par ? o2 : o1, W, false, T, W, l.ff, fs), "feed-forward down");
         } else if (l.ff > 0) {
             const int ldg = ld8(2 * l.ff), ldf = ld8(l.ff);
-            STEP(linear(m, xa, W, l.ff_in, nullptr, proj, ldg, false, T, 2 * l.ff, W, s), "feed-forward in");
-            STEP(lcc::glu_gelu_tanh(dt, proj, ldg, mid, ldf, T, l.ff, s), "gated gelu");
-            STEP(linear(m, mid, ldf, l.ff_out, nullptr, par ? o2 : o1, W, false, T, W, l.ff, s), "feed-forward out");
+            STEP(linear(m, xa, W, l.ff_in, nullptr, proj, ldg, false, T, 2 * l.ff, W, fs), "feed-forward in");
+            STEP(lcc::glu_gelu_tanh(dt, proj, ldg, mid, ldf, T, l.ff, fs), "gated gelu");
+            STEP(linear(m, mid, ldf, l.ff_out, nullptr, par ? o2 : o1, W, false, T, W, l.ff, fs), "feed-forward out");
         }
+        if (fork_ff && (cudaEventRecord(m->ev_join, m->side) != cudaSuccess || cudaStreamWaitEvent(s, m->ev_join, 0) != cudaSuccess))
+            LCC_FAIL(m->ctx, -100, "stream join failed");
         if (par) {
             // x <- x + (mixer + feed-forward), then the next layer's norm of the new row
             STEP(lcc::residual_norm(dt, x32, o1, W, (has_ff && !par_is_mc) ? o2 : nullptr, W, par_is_mc ? &par_mc : nullptr, norm_of(li + 1),
