@@ -363,10 +363,17 @@ class SeqModelConfig:
                 else:
                     raise NotImplementedError(f"layer {i}: feed-forward kind {kind!r} is not supported")
             share = L.get("weights_of")
-            if share is not None:
+            if share is not None:        # follow the reference to the layer that owns the tensors
+                seen = {i}
                 share = int(share)
-                if not 0 <= share < i or d["layers"][share].get("weights_of") is not None:
-                    raise ValueError(f"layer {i}: weights_of must name an earlier layer that owns its tensors")
+                while True:
+                    if not 0 <= share < len(d["layers"]) or share in seen:
+                        raise ValueError(f"layer {i}: weights_of must lead to a layer that owns its tensors")
+                    nxt = d["layers"][share].get("weights_of")
+                    if nxt is None:
+                        break
+                    seen.add(share)
+                    share = int(nxt)
             if L["type"] == "attention":
                 if "attention" not in fam:
                     raise NotImplementedError(f"layer {i}: {arch} has no mixer of type 'attention'")

@@ -99,8 +99,8 @@ class SeqWeights:
         hc = cfg.block == "prenorm_hc"
         self.layers: List[dict] = []
         for i, L in enumerate(cfg.layers):
-            if L.weights_of >= 0:            # the layer runs with another layer's tensors (its cache and state are its own)
-                self.layers.append(self.layers[L.weights_of])
+            if L.weights_of >= 0:            # the layer runs with another layer's tensors (its cache and state are its own):
+                self.layers.append(None)     # filled in below, once every owner is built
                 continue
             p = f"l{i}."
             w = {"norm1": norm_w(p + "norm1")}
@@ -242,6 +242,9 @@ class SeqWeights:
                     w["ff_in"] = mat(p + "mlp.gate", p + "mlp.up")
                 w["ff_out"] = mat(p + "mlp.down")
             self.layers.append(w)
+        for i, L in enumerate(cfg.layers):
+            if L.weights_of >= 0:
+                self.layers[i] = self.layers[L.weights_of]
         self.unused = sorted(set(t) - used)
 
     def nbytes(self) -> int:

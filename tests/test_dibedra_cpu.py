@@ -50,7 +50,8 @@ def test_bad_configurations_are_refused():
     bad(lambda d: d["layers"][0]["mixer"]["rot"].update(dims=3))                   # pairs
     bad(lambda d: d["layers"][0]["mlp"]["router"]["groups"].update(count=4))       # 9 outputs in 4 groups
     bad(lambda d: (d["layers"][0]["mlp"]["router"]["groups"].update(keep=1), d["layers"][0]["mlp"]["router"].update(top=4)))   # 3 kept, 4 wanted
-    bad(lambda d: d["layers"][1].update(weights_of=2))                             # a later layer
+    bad(lambda d: d["layers"][1].update(weights_of=1))                             # itself
+    bad(lambda d: d["layers"][1].update(weights_of=7))                             # no such layer
     bad(lambda d: d["layers"][0].update(type="mamba3"))
 
 

@@ -196,6 +196,12 @@ def test_layers_that_share_weights_keep_caches_of_their_own():
     m = build(d, tensors)
     assert rel(run(m, toks, []), want) < F32_TOL
     assert rel(run(m, toks, [60, 62] + list(range(63, 100))), want) < F32_TOL
+    # the owner may come later in the stack
+    d2 = K.config([K.shared(base, 0), K.att(heads=2, kv_heads=1, dim=8, window=50, mlp="dense")], width=16, vocab=40)
+    d2["layers"][0]["weights_of"] = 1
+    t2 = synthetic_seq_tensors(SeqModelConfig.from_json(d2), seed=28)
+    assert sorted({n.split(".")[0] for n in t2 if n.startswith("l")}) == ["l1"]
+    assert rel(run(build(d2, t2), toks, [50]), O.forward(d2, t2, toks)) < F32_TOL
 
 
 # ---- far keys, page borders, the window's edges ---------------------------------------------------------------------------
