@@ -292,10 +292,11 @@ int lcc_resize_bicubic_aa_u8(lcc_ctx* ctx, const lcc_resize_plan* plan, const ui
                              lcc_stream_t stream);
 
 /* ---- hybrid sequence models: decoder-only language models whose layers mix tokens with a state-space recurrence, gated
- * linear attention, retention, chunk-local attention or latent attention instead of (or beside) full attention. A layer is
+ * linear attention, retention, chunk-local attention, latent attention or sliding-window attention. A layer is
  *     x <- norm1(alpha * x + mixer(x)),  then (if it has a feed-forward)  x <- norm2(alpha * x + ff(x))       (post-norm)
- * or, in a model with LCC_BLOCK_PRENORM_HC, pre-norm sublayers on several residual streams (see LCC_BLOCK_PRENORM_HC);
- * the feed-forward is dense (gated gelu) or routed (LCC_FF_MOE);
+ * or, in a model with LCC_BLOCK_PRENORM_HC, pre-norm sublayers on several residual streams (see LCC_BLOCK_PRENORM_HC),
+ * or, with LCC_BLOCK_PARALLEL, x <- x + mixer(norm1(x)) + ff(norm1(x));
+ * the feed-forward is dense (gated gelu, or two matrices around a gelu) or routed (LCC_FF_MOE);
  * with the residual stream(s), every norm, every score, every router and every recurrent state in fp32. One library serves two storage
  * types: LCC_DT_BF16 (bf16 weights, activations and K/V pages; fp32 accumulation) and LCC_DT_F32 (everything fp32, plain
  * FMAs). The caller owns all memory: weights, workspace, K/V pages and the fp32 recurrent-state slots of every sequence. */

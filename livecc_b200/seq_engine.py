@@ -1,6 +1,6 @@
 """Hybrid sequence models (decoder-only language models built from state-space, gated-linear-attention, chunk-local
-attention, retention and latent-attention mixers, in post-norm blocks or pre-norm blocks on several residual streams, with
-dense or routed feed-forwards) behind the same surface as the video-language engine: `from_pretrained`, `generate`, a cache object that
+attention, retention, latent-attention and sliding-window attention mixers, in post-norm blocks, pre-norm blocks on several
+residual streams or parallel blocks, with dense or routed feed-forwards) behind the same surface as the video-language engine: `from_pretrained`, `generate`, a cache object that
 callers pass back, greedy token selection in the library's sampling kernel.
 
     model = SeqLMForCausalLM.from_pretrained(path, torch_dtype="bfloat16", device_map="cuda")
@@ -290,7 +290,7 @@ class SeqLMForCausalLM:
     @classmethod
     def from_pretrained(cls, model_path: str, torch_dtype="auto", device_map="cuda", max_tokens: int = 0, **_):
         """A directory with config.json and *.safetensors (bf16 tensors; names `embed`, `l<i>.norm1`, `l<i>.mix.*`,
-        `l<i>.mlp.*`, `final.norm`, `head`)."""
+        `l<i>.mlp.*`, `final.norm`, `head`; a Dynamic-Tanh norm adds `<norm>.b` and `<norm>.alpha`)."""
         from .checkpoint import iter_safetensors
 
         with open(os.path.join(model_path, "config.json")) as f:

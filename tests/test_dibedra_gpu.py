@@ -121,7 +121,7 @@ def test_the_window_the_correction_and_the_groups_show_in_these_weights():
 
 def test_identity_experts_return_the_normed_row():
     """Every router output but one is an identity expert and the correction forces the choice onto them: the feed-forward
-    is then (sum of the chosen scores) x the normed row, exactly; and with the correction the other way round, only the one
+    is then (sum of the chosen scores) x the normed row, exactly; and with the correction reversed, only the one
     real expert is chosen."""
     d = K.config([K.att(mlp=K.moe(experts=1, top=2, ff=8, limit=1.0, identity=3))], width=16, vocab=40)
     for force_identity in (True, False):
