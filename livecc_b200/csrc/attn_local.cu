@@ -47,7 +47,16 @@ __device__ __forceinline__ float gate_of(const T* gate, int ld_gate, int t, int 
 // row's heads over several CTAs). Per head: sum of squares over D -> the
 // normed channels -> rotation of the first rot_dims channels -> q_out, or the K page; the V page takes its columns of the
 // row as they are.
-template <typename T>
+template <typename T> __device__ __forceinline__ float2 ld2(const T* p);
+template <> __device__ __forceinline__ float2 ld2<float>(const float* p) { return *reinterpret_cast<const float2*>(p); }
+template <> __device__ __forceinline__ float2 ld2<bf16>(const bf16* p) { return unpack_bf16x2(*reinterpret_cast<const uint32_t*>(p)); }
+template <typename T> __device__ __forceinline__ void st2(T* p, float a, float b);
+template <> __device__ __forceinline__ void st2<float>(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+template <> __device__ __forceinline__ void st2<bf16>(bf16* p, float a, float b) { *reinterpret_cast<uint32_t*>(p) = pack_bf16x2(a, b); }
+
+// PAIRS: the pair-interleaved layout with an even head size and aligned rows: a lane owns neighbouring channels (2j, 2j+1), which
+// are one load, one angle, one sincosf and one store; a head of up to 256 channels stays in registers between the two passes.
+template <typename T, bool PAIRS>
 __global__ void __launch_bounds__(256) qk_headnorm_rope_append_kernel(const T* __restrict__ proj, int ld, int v_col,
                                                                       const float* __restrict__ qn_w, const float* __restrict__ kn_w,
                                                                       float eps, const float* __restrict__ inv_freq, float mag,
@@ -68,6 +77,38 @@ __global__ void __launch_bounds__(256) qk_headnorm_rope_append_kernel(const T* _
         const T* x = row + (size_t)hd * D;                 // k heads follow the q heads in the row
         const float* w = is_q ? qn_w : kn_w;
         float ss = 0.f;
+        if (PAIRS) {
+            constexpr int kKeep = 4;                       // pairs a lane keeps: heads of up to 256 channels
+            const int np = D >> 1;
+            float2 keep[kKeep];
+#pragma unroll
+            for (int u = 0; u < kKeep; ++u) {
+                const int j = lane + 32 * u;
+                keep[u] = j < np ? ld2(x + 2 * j) : make_float2(0.f, 0.f);
+                ss = fmaf(keep[u].x, keep[u].x, fmaf(keep[u].y, keep[u].y, ss));
+            }
+            for (int j = lane + 32 * kKeep; j < np; j += 32) { const float2 v = ld2(x + 2 * j); ss = fmaf(v.x, v.x, fmaf(v.y, v.y, ss)); }
+            ss = warp_sum(ss);
+            const float rn = w ? 1.f / sqrtf(ss / (float)D + eps) : 1.f;
+            float* qo = q_out + ((size_t)t * Hq + hd) * D;
+            T* ko = k_pages + (((size_t)page * G + (hd - Hq)) * page_size + slot) * D;
+            auto emit = [&](int j, const float2 v) {
+                float a = v.x * rn * (w ? w[2 * j] : 1.f), b = v.y * rn * (w ? w[2 * j + 1] : 1.f);
+                if (2 * j < rot_dims) {
+                    float sn, cs;
+                    sincosf(pf * inv_freq[j], &sn, &cs);
+                    sn *= mag; cs *= mag;
+                    const float ra = a * cs - b * sn, rb = b * cs + a * sn;
+                    a = ra; b = rb;
+                }
+                if (is_q) st2(qo + 2 * j, a, b); else st2(ko + 2 * j, a, b);
+            };
+#pragma unroll
+            for (int u = 0; u < kKeep; ++u)
+                if (lane + 32 * u < np) emit(lane + 32 * u, keep[u]);
+            for (int j = lane + 32 * kKeep; j < np; j += 32) emit(j, ld2(x + 2 * j));
+            continue;
+        }
         for (int c = lane; c < D; c += 32) { const float v = ldf(x + c); ss = fmaf(v, v, ss); }
         ss = warp_sum(ss);
         const float rn = w ? 1.f / sqrtf(ss / (float)D + eps) : 1.f;
@@ -902,14 +943,16 @@ int qk_headnorm_rope_append(int dt, const void* proj, int ld, int v_col, const f
     // many rows: 8 warps walk a row's heads; few rows: 4-warp CTAs, one head per warp, so that a decode step fills more SMs
     const int threads = S >= 64 ? 256 : 128;
     const dim3 grid(S, S >= 64 ? 1 : (Hq + G + 3) / 4);
-    if (dt == DT_F32)
-        qk_headnorm_rope_append_kernel<float><<<grid, threads, 0, s>>>((const float*)proj, ld, v_col, qn_w, kn_w, eps, inv_freq, mag, rot_dims,
-                                                                rot_pairs, q_out, (float*)k_pages, (float*)v_pages, page_table, page_size,
-                                                                S, Hq, G, D, DV, pos);
-    else
-        qk_headnorm_rope_append_kernel<bf16><<<grid, threads, 0, s>>>((const bf16*)proj, ld, v_col, qn_w, kn_w, eps, inv_freq, mag, rot_dims,
-                                                               rot_pairs, q_out, (bf16*)k_pages, (bf16*)v_pages, page_table, page_size,
-                                                               S, Hq, G, D, DV, pos);
+    const size_t es = dt == DT_F32 ? 4 : 2;
+    const bool pairs = (rot_pairs || rot_dims == 0) && (D % 2) == 0 && (ld % 2) == 0 && ((uintptr_t)proj % (2 * es)) == 0 &&
+                       ((uintptr_t)k_pages % (2 * es)) == 0 && ((uintptr_t)q_out % 8) == 0;
+#define LCC_APPEND(T, P)                                                                                                      \
+    qk_headnorm_rope_append_kernel<T, P><<<grid, threads, 0, s>>>((const T*)proj, ld, v_col, qn_w, kn_w, eps, inv_freq, mag, rot_dims,  \
+                                                                  rot_pairs, q_out, (T*)k_pages, (T*)v_pages, page_table, page_size, S, Hq, \
+                                                                  G, D, DV, pos)
+    if (dt == DT_F32) { if (pairs) LCC_APPEND(float, true); else LCC_APPEND(float, false); }
+    else { if (pairs) LCC_APPEND(bf16, true); else LCC_APPEND(bf16, false); }
+#undef LCC_APPEND
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }
 
