@@ -646,8 +646,10 @@ __device__ __forceinline__ void stage_bf16_rows(bf16* dst, int ld_dst, int ncp, 
     }
 }
 
-template <bool VEC8, int KH, int NV>
-__global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pages,
+// NBUF (VEC8 only): 2 = the next tile's copies fly while this one is computed; 1 = one buffer, which halves the shared memory so
+// that two CTAs share an SM and hide each other's copies and tensor-pipe latency instead.
+template <bool VEC8, int KH, int NV, int NBUF = 2>
+__global__ void __launch_bounds__(128 * KH, (VEC8 && NBUF == 1) ? 2 : 0) attn_chunk_sink_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pages,
                                                                   const bf16* __restrict__ v_pages, const int* __restrict__ page_table,
                                                                   int page_size, const bf16* __restrict__ gate, int ld_gate,
                                                                   bf16* __restrict__ out, int ld_out, int S, int Hq, int G, int D, int DV,
@@ -661,7 +663,7 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
     bf16* sQ = reinterpret_cast<bf16*>(smem_attn);     // [MQ][LQ]
     constexpr int KT = KH * MK;                         // keys per step of the CTA: one 64-key tile per group of 4 warps
     bf16* sK0 = sQ + (size_t)MQ * LQ;                   // [2][KT][LQ]   (the second buffer only with VEC8)
-    bf16* sV0 = sK0 + (size_t)(VEC8 ? 2 : 1) * KT * LQ; // [2][KT][MLV]
+    bf16* sV0 = sK0 + (size_t)(VEC8 ? NBUF : 1) * KT * LQ; // [2][KT][MLV]
     const int t0 = (gridDim.y - 1 - blockIdx.y) * MQ, h = blockIdx.x, c0 = blockIdx.z * MVW;
     const int g = h / (Hq / G);
     const int past = seq_past(pos, S);
@@ -717,14 +719,19 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
         }
         cp_async_commit();
     };
-    if (VEC8) issue(kbeg, 0);
+    if (VEC8 && NBUF == 2) issue(kbeg, 0);
     int it = 0;
     for (int kc = kbeg; kc <= pl; kc += KT, ++it) {
-        const int buf = VEC8 ? (it & 1) : 0;
+        const int buf = (VEC8 && NBUF == 2) ? (it & 1) : 0;
         const int k0 = kc + kh * MK;                    // this group of warps' tile of the step
         const bf16* sK = sK0 + ((size_t)buf * KT + kh * MK) * LQ;
         const bf16* sV = sV0 + ((size_t)buf * KT + kh * MK) * MLV;
-        if (VEC8) {
+        if (VEC8 && NBUF == 1) {
+            __syncthreads();       // every thread is done with the previous tile (and Q is staged)
+            issue(kc, 0);
+            cp_async_wait<0>();
+            __syncthreads();
+        } else if (VEC8) {
             cp_async_wait<0>();
             __syncthreads();       // this tile has landed for every thread, and every thread is done with the other buffer
             if (kc + KT <= pl) issue(kc + KT, buf ^ 1);
@@ -872,7 +879,9 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
 int launch_attn_mma(const float* q, const void* k_pages, const void* v_pages, const int* page_table, int page_size,
                     const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D, int DV, int chunk,
                     float scale, SeqPos pos, cudaStream_t s, const float* sink, int ld_v, AttnOpts opt) {
-    static SmemAttrOnce once82, once81, once1, once81w, once1w;
+    static SmemAttrOnce once82, once82s, once81, once1, once81w, once1w;
+    // two groups of warps: one K/V buffer and two CTAs per SM (default), or two buffers and one CTA (LIVECC_B200_SEQ_ATTN_NBUF=2)
+    static const int nbuf2 = [] { const char* e = getenv("LIVECC_B200_SEQ_ATTN_NBUF"); return e ? atoi(e) : 1; }();
     const int Dp = (D + 15) / 16 * 16;
     // 16-byte copies need every K and V row (and the output-channel slice) to start on a 16-byte boundary
     const bool vec8 = (D % 8) == 0 && (DV % 8) == 0 && (ld_v % 8) == 0 && ((uintptr_t)k_pages % 16) == 0 && ((uintptr_t)v_pages % 16) == 0;
@@ -881,19 +890,20 @@ int launch_attn_mma(const float* q, const void* k_pages, const void* v_pages, co
     // values wider than 128 channels: two output tiles per CTA against one pass over the scores (one group of warps)
     const bool wide = DV > 128;
     const bool two = vec8 && Dp <= 128 && !wide;
-    const int nbuf = vec8 ? 2 : 1, kh = two ? 2 : 1, MVW = wide ? 256 : 128, MLV = MVW + 8;
+    const int nbuf = vec8 ? ((two && nbuf2 == 1) ? 1 : 2) : 1, kh = two ? 2 : 1, MVW = wide ? 256 : 128, MLV = MVW + 8;
     auto bytes = [&](int dp) { return ((size_t)MQ * (dp + 8) + (size_t)nbuf * kh * MK * (dp + 8 + MLV)) * sizeof(bf16); };
     const size_t smem = bytes(Dp), smem_max = bytes(two ? 128 : kAttnMmaMaxDim);
     dim3 grid(Hq, (S + MQ - 1) / MQ, (DV + MVW - 1) / MVW);
     count_launch();
-#define LCC_ATTN_MMA(ONCE, VEC, KHN, NVN)                                                                                       \
+#define LCC_ATTN_MMA(ONCE, VEC, KHN, NVN, ...)                                                                                  \
     do {                                                                                                                     \
-        if (ensure_dyn_smem(ONCE, attn_chunk_sink_mma_kernel<VEC, KHN, NVN>, (int)smem_max)) return -100;                         \
-        attn_chunk_sink_mma_kernel<VEC, KHN, NVN><<<grid, 128 * KHN, smem, s>>>(q, (const bf16*)k_pages, (const bf16*)v_pages, page_table, \
+        if (ensure_dyn_smem(ONCE, attn_chunk_sink_mma_kernel<VEC, KHN, NVN, ##__VA_ARGS__>, (int)smem_max)) return -100;          \
+        attn_chunk_sink_mma_kernel<VEC, KHN, NVN, ##__VA_ARGS__><<<grid, 128 * KHN, smem, s>>>(q, (const bf16*)k_pages, (const bf16*)v_pages, page_table, \
                                                                            page_size, (const bf16*)gate, ld_gate, (bf16*)out, ld_out, \
                                                                            S, Hq, G, D, DV, chunk, scale, pos, sink, ld_v, opt);  \
     } while (0)
-    if (two) LCC_ATTN_MMA(once82, true, 2, 1);
+    if (two && nbuf == 1) LCC_ATTN_MMA(once82s, true, 2, 1, 1);
+    else if (two) LCC_ATTN_MMA(once82, true, 2, 1);
     else if (wide && vec8) LCC_ATTN_MMA(once81w, true, 1, 2);
     else if (wide) LCC_ATTN_MMA(once1w, false, 1, 2);
     else if (vec8) LCC_ATTN_MMA(once81, true, 1, 1);
