@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define LCC_ABI_VERSION 10
+#define LCC_ABI_VERSION 11
 #define LCC_PAGE_SIZE 64
 
 typedef struct lcc_ctx lcc_ctx;
@@ -295,7 +295,9 @@ int lcc_resize_bicubic_aa_u8(lcc_ctx* ctx, const lcc_resize_plan* plan, const ui
  * linear attention, retention, chunk-local attention, latent attention or sliding-window attention. A layer is
  *     x <- norm1(alpha * x + mixer(x)),  then (if it has a feed-forward)  x <- norm2(alpha * x + ff(x))       (post-norm)
  * or, in a model with LCC_BLOCK_PRENORM_HC, pre-norm sublayers on several residual streams (see LCC_BLOCK_PRENORM_HC),
- * or, with LCC_BLOCK_PARALLEL, x <- x + mixer(norm1(x)) + ff(norm1(x));
+ * or, with LCC_BLOCK_PARALLEL, x <- x + mixer(norm1(x)) + ff(norm1(x)),
+ * or, with LCC_BLOCK_BRANCHNORM, x <- x + norm1(mixer(x + canon(x))), then x <- x + norm2(ff(x)) (the norm sits on the sublayer's
+ * output; canon is a short causal convolution over time on every channel of the residual stream);
  * the feed-forward is dense (gated gelu, or two matrices around a gelu) or routed (LCC_FF_MOE);
  * with the residual stream(s), every norm, every score, every router and every recurrent state in fp32. One library serves two storage
  * types: LCC_DT_BF16 (bf16 weights, activations and K/V pages; fp32 accumulation) and LCC_DT_F32 (everything fp32, plain
@@ -309,6 +311,9 @@ int lcc_resize_bicubic_aa_u8(lcc_ctx* ctx, const lcc_resize_plan* plan, const ui
 #define LCC_MIX_ATTENTION 5 /* softmax attention over paged K/V: per-head q/k RMS norm, rotary positions on part of a head, a sliding
                                window and / or chunks, optional sink, values projected or taken from the keys as projected, output
                                gate per head or per channel (every option a field of the layer) */
+#define LCC_MIX_DELTA 6     /* gated delta rule with a decay per key channel: q/k/v through a short causal convolution + silu, unit-length q
+                               and k, S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q; unit-rms heads x weight x sigmoid
+                               gate -> out-proj (decays and output gate come through low-rank bottlenecks) */
 #define LCC_FF_GLU 0        /* dense gated feed-forward: gelu_tanh(gate) * up */
 #define LCC_FF_MOE 1        /* routed experts (sigmoid or softmax router, top-k of score + correction, optionally inside the best groups
                                of neighbouring experts; relu^2 or clamped gated experts; identity experts) + gated shared expert */
@@ -317,12 +322,15 @@ int lcc_resize_bicubic_aa_u8(lcc_ctx* ctx, const lcc_resize_plan* plan, const ui
 #define LCC_BLOCK_PRENORM_HC 1 /* `streams` residual streams x_s; per sublayer: u = sum_s in[s] x_s; y = sublayer(norm(u));
                                   x_t <- sum_s mix[s][t] x_s + out[t] y. The model's output is the sum of the streams. */
 #define LCC_BLOCK_PARALLEL 2   /* h = norm1(x); x <- x + mixer(h) + ff(h): one norm, both sublayers read it, one fp32 residual sum */
+#define LCC_BLOCK_BRANCHNORM 3 /* x <- x + norm1(mixer(x + canon(x))); x <- x + norm2(ff(x)): sublayers read the residual stream itself */
 #define LCC_NORM_RMS 0         /* x / sqrt(mean(x^2) + eps) * w */
 #define LCC_NORM_DYT 1         /* tanh(alpha * x) * w + b: no statistics of the row (Dynamic Tanh) */
 #define LCC_ROUTER_SIGMOID 0
 #define LCC_ROUTER_SOFTMAX 1   /* scores = softmax over all router outputs (identity experts included) */
+#define LCC_ROUTER_TOPK_SOFTMAX 2 /* the e_top largest logits are chosen; weights = softmax over the chosen logits only */
 #define LCC_EXPERT_RELU2 0     /* down(relu(up x)^2) */
 #define LCC_EXPERT_CLAMP_GLU 1 /* g = min(gate x, limit), u = clamp(up x, +-limit); down(g * sigmoid(1.702 g) * (u + 1)); e_up rows [gate | up] */
+#define LCC_EXPERT_SILU_GLU 2  /* down(silu(gate x) * (up x)); e_up rows as for LCC_EXPERT_CLAMP_GLU */
 #define LCC_GATE_NONE 0
 #define LCC_GATE_HEAD 1        /* one sigmoid gate per (row, head) */
 #define LCC_GATE_CHANNEL 2     /* one sigmoid gate per (row, head, value channel) */
@@ -345,6 +353,10 @@ typedef struct {
      * and reads that layer's */
     int32_t a_heads, a_dim, a_rot_dim, a_vdim, a_rank, a_kv_from;
     float a_scale;
+    /* a_q_rank > 0: the queries come through a latent of that many channels (a_in rows [q latent | latent, key part | gate], RMS norm
+     * with a_q_norm_f32, then a_uq); a_window > 0: a row at position i sees j with i - j < a_window; a_gate: a_in ends with one gate
+     * row per head; a_sink_f32 NULL: ordinary softmax */
+    int32_t a_q_rank, a_window, a_gate;
     float rot_mag;  /* factor on cos and sin of the rotation (1 without long-context scaling) */
     /* LCC_MIX_ATTENTION: m_heads query heads over m_kv_heads key/value heads; per-head RMS norm of q and k (weights [m_dim], shared by
      * the heads); the first m_rot_dims channels of a head rotated (m_rot_pairs: channel 2i with 2i+1, else i with i + dims/2);
@@ -353,6 +365,14 @@ typedef struct {
      * (before norm and rotation; the layer has no value projection); m_gate: LCC_GATE_* */
     int32_t m_heads, m_kv_heads, m_dim, m_vdim, m_window, m_chunk, m_rot_dims, m_rot_pairs, m_sink, m_value_keys, m_gate;
     float m_scale;
+    /* m_unit_norm: q and k heads are divided by their rms without a weight (m_qnorm_f32 / m_knorm_f32 NULL); m_temp_f32: one factor
+     * per query head on the scores; m_vmix_role: 0 none, 1 the layer's values as projected are kept for later layers of the step, 2 the
+     * cached values are (1 - m_vmix) * v + m_vmix * the kept values of the same token */
+    int32_t m_unit_norm, m_vmix_role;
+    float m_vmix;
+    /* LCC_MIX_DELTA: d_heads value heads of d_vdim channels over d_kv_heads query/key heads of d_dim channels, d_conv taps, bottleneck
+     * ranks of the decay and of the output gate */
+    int32_t d_heads, d_kv_heads, d_dim, d_vdim, d_conv, d_rank_a, d_rank_g;
     /* feed-forward: ff_kind LCC_FF_*; MoE: e_experts experts of width e_ff, e_top per token, weights = score * e_scale,
      * shared expert of width e_shared_ff (0 = none) */
     int32_t ff_kind, e_experts, e_top, e_ff, e_shared_ff;
@@ -367,6 +387,17 @@ typedef struct {
     float norm1_alpha; /* LCC_NORM_DYT: the scalar inside tanh */
     /* weights: matrices [out, in] in the model's storage type; everything named *_f32 is fp32 */
     const float *norm1_f32, *norm2_f32;
+    const float* canon_w_f32;  /* LCC_BLOCK_BRANCHNORM: [width, canon_taps] taps of the convolution in front of the mixer (NULL: none) */
+    const float* m_temp_f32;   /* [m_heads] or NULL */
+    const void* a_uq;          /* [heads*(dim+rot_dim), a_q_rank] */
+    const float* a_q_norm_f32; /* [a_q_rank] */
+    const void* d_in;          /* [2*G*dim + heads*vdim + heads + rank_a + rank_g, width], rows [q | k | v | beta | decay-down | gate-down] */
+    const float* d_conv_w_f32; /* [2*G*dim + heads*vdim, d_conv], rows as q, k, v */
+    const void* d_a_up;        /* [heads*dim, rank_a] */
+    const float *d_dt_bias_f32, *d_a_log_f32; /* [heads*dim], [heads] */
+    const void* d_g_up;        /* [heads*vdim, rank_g] */
+    const float* d_norm_f32;   /* [vdim], shared by the heads */
+    const void* d_out;         /* [width, heads*vdim] */
     const float* norm1_bias_f32; /* LCC_NORM_DYT: [width] */
     const void* m_in;          /* [Hq*dim + G*dim (+ G*vdim) + gate rows, width], rows [q | k | (v) | gate] */
     const float *m_qnorm_f32, *m_knorm_f32; /* [dim] each */
@@ -402,7 +433,7 @@ typedef struct {
     const float* a_sink_f32;   /* [heads] sink logits */
     const void* a_out;         /* [width, heads*vdim] */
     const void* e_router;      /* [experts + identity (+1), width]: router rows, then the shared expert's gate row */
-    const float* e_correction_f32; /* [experts + identity]: added to the scores for the choice only */
+    const float* e_correction_f32; /* [experts + identity]: added to the scores for the choice only (NULL: zeros) */
     const void* e_up;          /* [experts][e_ff, width]; LCC_EXPERT_CLAMP_GLU: [experts][2*e_ff, width], rows [gate | up] */
     const void* e_down;        /* [experts][width, e_ff] */
     const void* e_shared_up;   /* [e_shared_ff, width] */
@@ -418,6 +449,7 @@ typedef struct {
     int32_t block;   /* LCC_BLOCK_* */
     int32_t streams; /* residual streams of LCC_BLOCK_PRENORM_HC (>= 1) */
     int32_t norm_kind; /* LCC_NORM_*: the block norms and the final norm */
+    int32_t canon_taps; /* LCC_BLOCK_BRANCHNORM: taps of the convolution in front of every mixer (<= 8) */
     float final_norm_alpha; /* LCC_NORM_DYT */
     float logit_scale;      /* logits are multiplied by it (0 reads as 1) */
     const float* final_norm_bias_f32; /* LCC_NORM_DYT: [width] */
@@ -430,7 +462,9 @@ typedef struct {
 
 /* One sequence's part of a step: n_new tokens that follow `past` cached ones. layer_state[i]: this sequence's fp32 state
  * slot of layer i (SSD: [conv carry: channels x (conv-1)] then [heads x vdim x state]; PARALLEL: [heads x vdim x dim] of
- * the right mixer; RETENTION: [heads x vdim x dim]), zero at the start of a sequence. k_pages[i] / v_pages[i]: the layer's page pools
+ * the right mixer; RETENTION: [heads x vdim x dim]; DELTA: [conv carry: channels x (conv-1)] then [heads x vdim x dim]; in a
+ * LCC_BLOCK_BRANCHNORM model every layer's slot starts with [width x (canon_taps-1)], the last inputs of the convolution in front of
+ * the mixer), zero at the start of a sequence. k_pages[i] / v_pages[i]: the layer's page pools
  * [page][kv_heads][page_size][dim|vdim] (NULL for layers without attention); a LATENT layer has K pages only,
  * [page][1][page_size][rank + rot_dim], and a layer that reads another layer's cache is given that layer's pool.
  * page_table: logical -> physical page.
@@ -448,6 +482,8 @@ typedef struct {
 } lcc_seq_entry;
 
 typedef struct lcc_seq_model lcc_seq_model;
+/* sizeof(lcc_seq_layer) (which = 0), sizeof(lcc_seq_model_desc) (1), sizeof(lcc_seq_entry) (2): a binding checks its own layout against them */
+size_t lcc_seq_struct_bytes(int which);
 lcc_seq_model* lcc_seq_model_create(lcc_ctx* ctx, const lcc_seq_model_desc* desc);
 void lcc_seq_model_destroy(lcc_seq_model* m);
 size_t lcc_seq_workspace_bytes(const lcc_seq_model* m, int max_tokens, int max_want);

@@ -13,7 +13,7 @@ PKG_DIR = Path(__file__).resolve().parent
 LIB_PATH = PKG_DIR / "liblivecc_sm100a.so"
 HEADER_PATH = PKG_DIR.parent / "include" / "livecc_b200.h"
 
-ABI_VERSION = 10
+ABI_VERSION = 11
 PAGE_SIZE = 64
 
 # epilogue codes (LCC_EPI_*)
@@ -71,13 +71,18 @@ class SeqLayer(C.Structure):
                [("l_scale", C.c_float)] + [(n, C.c_int32) for n in ("r_heads", "r_dim", "r_vdim", "r_rank")] + \
                [("r_tau", C.c_float)] + \
                [(n, C.c_int32) for n in ("t_heads", "t_dim", "t_vdim", "t_rot_dims", "a_heads", "a_dim", "a_rot_dim", "a_vdim",
-                                         "a_rank", "a_kv_from")] + [("a_scale", C.c_float), ("rot_mag", C.c_float)] + \
+                                         "a_rank", "a_kv_from")] + [("a_scale", C.c_float)] + \
+               [(n, C.c_int32) for n in ("a_q_rank", "a_window", "a_gate")] + [("rot_mag", C.c_float)] + \
                [(n, C.c_int32) for n in ("m_heads", "m_kv_heads", "m_dim", "m_vdim", "m_window", "m_chunk", "m_rot_dims", "m_rot_pairs",
                                          "m_sink", "m_value_keys", "m_gate")] + [("m_scale", C.c_float)] + \
+               [(n, C.c_int32) for n in ("m_unit_norm", "m_vmix_role")] + [("m_vmix", C.c_float)] + \
+               [(n, C.c_int32) for n in ("d_heads", "d_kv_heads", "d_dim", "d_vdim", "d_conv", "d_rank_a", "d_rank_g")] + \
                [(n, C.c_int32) for n in ("ff_kind", "e_experts", "e_top", "e_ff", "e_shared_ff")] + [("e_scale", C.c_float)] + \
                [(n, C.c_int32) for n in ("e_router_kind", "e_identity", "e_groups", "e_keep", "e_act", "e_up_il16")] + \
                [("e_limit", C.c_float), ("norm1_alpha", C.c_float)] + \
-               [(n, C.c_void_p) for n in ("norm1_f32", "norm2_f32", "norm1_bias_f32", "m_in", "m_qnorm_f32", "m_knorm_f32", "m_out", "s_in", "s_conv_w_f32", "s_conv_b_f32", "s_dt_bias_f32",
+               [(n, C.c_void_p) for n in ("norm1_f32", "norm2_f32", "canon_w_f32", "m_temp_f32", "a_uq", "a_q_norm_f32", "d_in",
+                                          "d_conv_w_f32", "d_a_up", "d_dt_bias_f32", "d_a_log_f32", "d_g_up", "d_norm_f32", "d_out",
+                                          "norm1_bias_f32", "m_in", "m_qnorm_f32", "m_knorm_f32", "m_out", "s_in", "s_conv_w_f32", "s_conv_b_f32", "s_dt_bias_f32",
                                           "s_a_log_f32", "s_skip_f32", "s_norm_f32", "s_out", "l_in", "l_in_bias_f32", "l_in_bias",
                                           "l_qnorm_f32", "l_knorm_f32", "l_out", "l_branch_norm_f32", "r_in", "r_decay_up",
                                           "r_decay_bias_f32", "r_norm_f32", "r_out", "r_branch_norm_f32", "ff_in", "ff_out",
@@ -91,7 +96,7 @@ class SeqModelDesc(C.Structure):
     """lcc_seq_model_desc"""
     _fields_ = [("width", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("dtype", C.c_int32),
                 ("rows_padded8", C.c_int32), ("eps", C.c_float), ("alpha", C.c_float), ("embed_scale", C.c_float), ("logit_softcap", C.c_float),
-                ("block", C.c_int32), ("streams", C.c_int32), ("norm_kind", C.c_int32), ("final_norm_alpha", C.c_float),
+                ("block", C.c_int32), ("streams", C.c_int32), ("norm_kind", C.c_int32), ("canon_taps", C.c_int32), ("final_norm_alpha", C.c_float),
                 ("logit_scale", C.c_float), ("final_norm_bias_f32", C.c_void_p),
                 ("embed", C.c_void_p), ("inv_freq_f32", C.c_void_p), ("final_norm_f32", C.c_void_p), ("head", C.c_void_p),
                 ("layers", C.POINTER(SeqLayer))]
@@ -105,12 +110,12 @@ class SeqEntry(C.Structure):
 
 
 DT_BF16, DT_F32 = 0, 1
-MIX_SSD, MIX_PARALLEL, MIX_RETENTION, MIX_LATENT, MIX_ATTENTION = 1, 2, 3, 4, 5
+MIX_SSD, MIX_PARALLEL, MIX_RETENTION, MIX_LATENT, MIX_ATTENTION, MIX_DELTA = 1, 2, 3, 4, 5, 6
 FF_GLU, FF_MOE, FF_MLP = 0, 1, 2
-BLOCK_POSTNORM, BLOCK_PRENORM_HC, BLOCK_PARALLEL = 0, 1, 2
+BLOCK_POSTNORM, BLOCK_PRENORM_HC, BLOCK_PARALLEL, BLOCK_BRANCHNORM = 0, 1, 2, 3
 NORM_RMS, NORM_DYT = 0, 1
-ROUTER_SIGMOID, ROUTER_SOFTMAX = 0, 1
-EXPERT_RELU2, EXPERT_CLAMP_GLU = 0, 1
+ROUTER_SIGMOID, ROUTER_SOFTMAX, ROUTER_TOPK_SOFTMAX = 0, 1, 2
+EXPERT_RELU2, EXPERT_CLAMP_GLU, EXPERT_SILU_GLU = 0, 1, 2
 GATE_NONE, GATE_HEAD, GATE_CHANNEL = 0, 1, 2
 
 _libs = {}   # profile (None = the full library) -> CDLL
@@ -149,6 +154,7 @@ def _declare(lib: C.CDLL):
     sig("lcc_resize_plan_info", None, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int64)])
     sig("lcc_seq_model_create", C.c_void_p, [C.c_void_p, C.POINTER(SeqModelDesc)])
     sig("lcc_seq_model_destroy", None, [C.c_void_p])
+    sig("lcc_seq_struct_bytes", C.c_size_t, [C.c_int])
     sig("lcc_seq_workspace_bytes", C.c_size_t, [C.c_void_p, C.c_int, C.c_int])
     sig("lcc_seq_bind_workspace", C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int])
     sig("lcc_seq_layer_state_floats", C.c_int64, [C.c_void_p, C.c_int])
@@ -528,6 +534,10 @@ class SeqNativeModel:
     def __init__(self, ctx: Context, desc: SeqModelDesc, keepalive):
         self.ctx, self.lib = ctx, ctx.lib
         self._keep = keepalive
+        for which, st in enumerate((SeqLayer, SeqModelDesc, SeqEntry)):
+            if int(self.lib.lcc_seq_struct_bytes(which)) != C.sizeof(st):
+                raise LiveCCNativeError(f"{st.__name__} does not match the library's layout ({C.sizeof(st)} bytes here, "
+                                        f"{int(self.lib.lcc_seq_struct_bytes(which))} there)")
         self.handle = self.lib.lcc_seq_model_create(C.c_void_p(ctx.handle), C.byref(desc))
         if not self.handle:
             raise LiveCCNativeError(self.lib.lcc_last_error(C.c_void_p(ctx.handle)).decode())

@@ -322,8 +322,10 @@ def seq_param_specs(cfg) -> List[Tuple[str, Tuple[int, ...], str]]:
     par = getattr(cfg, "block", "postnorm") == "parallel"     # one norm per layer
     dyt = getattr(cfg, "norm", "rms") == "dyt"                # a norm is a weight, a bias and a scalar
 
+    nshape = () if getattr(cfg, "norm_scalar", False) else (W,)      # a norm whose weight is one number
+
     def norm_specs(name):
-        return [(name, (W,), norm)] + ([(name + ".b", (W,), "b"), (name + ".alpha", (), "alpha")] if dyt else [])
+        return [(name, nshape, norm)] + ([(name + ".b", (W,), "b"), (name + ".alpha", (), "alpha")] if dyt else [])
 
     for i, L in enumerate(cfg.layers):
         if getattr(L, "weights_of", -1) >= 0:                 # runs with another layer's tensors
@@ -331,7 +333,9 @@ def seq_param_specs(cfg) -> List[Tuple[str, Tuple[int, ...], str]]:
         p = f"l{i}."
         specs += norm_specs(p + "norm1")
         if (L.ff or L.moe) and not par:
-            specs.append((p + "norm2", (W,), norm))
+            specs.append((p + "norm2", nshape, norm))
+        if getattr(cfg, "canon_taps", 0):
+            specs.append((p + "canon1", (W, cfg.canon_taps), "canon"))
         if hc:
             n = cfg.streams
             for q in ("hc1.", "hc2.") if (L.ff or L.moe) else ("hc1.",):
@@ -340,17 +344,37 @@ def seq_param_specs(cfg) -> List[Tuple[str, Tuple[int, ...], str]]:
             t, m = L.retention, p + "mix."
             specs += [(m + "q", (t.heads * t.dim, W), "w"), (m + "k", (t.heads * t.dim, W), "w"), (m + "v", (t.heads * t.vdim, W), "w"),
                       (m + "g", (t.heads * t.vdim, W), "w"), (m + "o", (W, t.heads * t.vdim), "w")]
+        elif L.type == "channel_delta":
+            t, m = L.delta, p + "mix."
+            nk, nv = t.kv_heads * t.dim, t.heads * t.vdim
+            ra, rg = t.rank_a or max(4, t.dim // 4), t.rank_g or max(4, t.vdim // 4)
+            specs += [(m + "q", (nk, W), "w"), (m + "q.conv", (nk, t.conv), "conv"), (m + "k", (nk, W), "w"), (m + "k.conv", (nk, t.conv), "conv"),
+                      (m + "v", (nv, W), "w"), (m + "v.conv", (nv, t.conv), "conv"), (m + "b", (t.heads, W), "w"), (m + "A_log", (t.heads,), "alog"),
+                      (m + "norm", (t.vdim,), "norm"), (m + "a1", (ra, W), "w"), (m + "a2", (t.heads * t.dim, ra), "w"),
+                      (m + "dt_bias", (t.heads * t.dim,), "dt"), (m + "g1", (rg, W), "w"), (m + "g2", (nv, rg), "w"), (m + "o", (W, nv), "w")]
         elif L.type == "latent_attention":
             a, m = L.latent, p + "mix."
-            specs.append((m + "q", (a.heads * (a.dim + a.rot_dim), W), "w"))
+            if a.q_rank:
+                specs += [(m + "dq", (a.q_rank, W), "w"), (m + "dq.norm", (a.q_rank,), "norm"), (m + "uq", (a.heads * (a.dim + a.rot_dim), a.q_rank), "w")]
+            else:
+                specs.append((m + "q", (a.heads * (a.dim + a.rot_dim), W), "w"))
             if a.kv_from < 0:
                 specs += [(m + "dkv", (a.kv_rank + a.rot_dim, W), "w"), (m + "dkv.norm", (a.kv_rank,), "norm")]
-            specs += [(m + "uk", (a.heads * a.dim, a.kv_rank), "w"), (m + "uv", (a.heads * a.vdim, a.kv_rank), "w"),
-                      (m + "sink", (a.heads,), "skip"), (m + "g", (a.heads, W), "w"), (m + "o", (W, a.heads * a.vdim), "w")]
+            specs += [(m + "uk", (a.heads * a.dim, a.kv_rank), "w"), (m + "uv", (a.heads * a.vdim, a.kv_rank), "w")]
+            if a.sink:
+                specs.append((m + "sink", (a.heads,), "skip"))
+            if a.gate:
+                specs.append((m + "g", (a.heads, W), "w"))
+            specs.append((m + "o", (W, a.heads * a.vdim), "w"))
         elif L.type == "attention":
             a, m = L.attn, p + "mix."
-            specs += [(m + "q", (a.heads * a.dim, W), "w"), (m + "k", (a.kv_heads * a.dim, W), "w"),
-                      (m + "q.norm", (a.dim,), "norm"), (m + "k.norm", (a.dim,), "norm")]
+            specs += [(m + "q", (a.heads * a.dim, W), "w"), (m + "k", (a.kv_heads * a.dim, W), "w")]
+            if not a.unit_norm:
+                specs += [(m + "q.norm", (a.dim,), "norm"), (m + "k.norm", (a.dim,), "norm")]
+            if a.temp:
+                specs.append((m + "temp", (a.heads,), "skip"))
+            if a.v_mix:
+                specs.append((m + "vmix", (), "mix"))
             if not a.value_keys:
                 specs.append((m + "v", (a.kv_heads * a.vdim, W), "w"))
             if a.gate != "none":
@@ -378,10 +402,12 @@ def seq_param_specs(cfg) -> List[Tuple[str, Tuple[int, ...], str]]:
         if L.moe:
             e, m = L.moe, p + "mlp."
             for j in range(e.experts):
-                if e.act == "clamp_glu":
+                if e.act in ("clamp_glu", "silu_glu"):
                     specs.append((f"{m}e{j}.gate", (e.ff, W), "w"))
                 specs += [(f"{m}e{j}.up", (e.ff, W), "w"), (f"{m}e{j}.down", (W, e.ff), "w")]
-            specs += [(m + "router", (e.outputs, W), "w"), (m + "correction", (e.outputs,), "b")]
+            specs.append((m + "router", (e.outputs, W), "w"))
+            if e.router != "topk_softmax":
+                specs.append((m + "correction", (e.outputs,), "b"))
             if e.shared_ff:
                 specs += [(m + "shared.up", (e.shared_ff, W), "w"), (m + "shared.down", (W, e.shared_ff), "w"),
                           (m + "shared.sg", (1, W), "w")]
@@ -421,6 +447,10 @@ def synthetic_seq_tensors(cfg, seed: int = 1234, device="cpu") -> Dict[str, torc
             t = torch.eye(shape[0], device=u.device) + 0.4 * u
         elif kind == "conv":
             t = u * 1.5
+        elif kind == "canon":
+            t = u * 0.8
+        elif kind == "mix":
+            t = 0.5 + 0.6 * u
         elif kind == "dt":
             t = u * 4.0 - 2.0
         elif kind == "alog":

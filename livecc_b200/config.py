@@ -240,6 +240,10 @@ class LatentAttnConfig:
     scale: float
     rot: RotaryConfig
     kv_from: int = -1
+    q_rank: int = 0       # > 0: the queries come through a latent of that many channels (RMS norm with a weight, then an up-projection)
+    window: int = 0       # > 0: row i sees j with 0 <= i - j < window
+    gate: bool = True     # the per-head sigmoid gate
+    sink: bool = True     # the per-head sink logit (False: ordinary softmax)
 
 
 @dataclass
@@ -249,8 +253,9 @@ class MoeConfig:
     `router`: "sigmoid" (a score per expert) or "softmax" (over all router outputs). The last `identity` router outputs
     (beyond `experts`) stand for experts that return their input. `groups` > 0: the router outputs form that many equal
     groups of neighbours, a group scores as its best choice score, and only members of the best `keep` groups can be chosen.
-    `act`: "relu2" (down(relu(up x)^2)) or "clamp_glu" (g = min(gate x, limit), u = clamp(up x, -limit, limit),
-    down(g sigmoid(1.702 g) (u + 1)))."""
+    `act`: "relu2" (down(relu(up x)^2)), "clamp_glu" (g = min(gate x, limit), u = clamp(up x, -limit, limit),
+    down(g sigmoid(1.702 g) (u + 1))) or "silu_glu" (down(silu(gate x) * (up x))). `router` "topk_softmax": the `top` largest
+    logits are chosen and weighted by the softmax over the chosen logits only (no correction tensor)."""
     experts: int
     top: int
     ff: int
@@ -287,6 +292,9 @@ class MaskedAttnConfig:
     value_keys: bool = True
     gate: str = "channel"
     sink: bool = False
+    unit_norm: bool = False   # q and k heads are divided by their rms without a weight (no q.norm / k.norm tensors)
+    temp: bool = False        # a learned factor per query head on the scores (tensor `temp`)
+    v_mix: bool = False       # the cached values are (1 - vmix) v + vmix v_first, v_first = the first such layer's values of the token
 
     @property
     def gate_rows(self) -> int:
@@ -294,8 +302,28 @@ class MaskedAttnConfig:
 
 
 @dataclass
+class DeltaConfig:
+    """Gated delta rule with a decay per head and key channel: q, k (kv_heads x dim) and v (heads x vdim) pass a causal
+    convolution of `conv` taps and silu; q and k become unit vectors per head (q also times dim^-1/2); per head
+    S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q with beta = sigmoid(b x) and
+    g = exp(-exp(A_log) softplus(a2 (a1 x) + dt_bias)); each head's o is brought to unit rms, times a weight of vdim channels,
+    times sigmoid(g2 (g1 x)). The bottleneck ranks come from the tensors' shapes when 0."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int = 4
+    rank_a: int = 0
+    rank_g: int = 0
+
+    @property
+    def conv_channels(self) -> int:
+        return 2 * self.kv_heads * self.dim + self.heads * self.vdim
+
+
+@dataclass
 class SeqLayerConfig:
-    type: str                      # "mamba2" | "parallel" | "retention" | "latent_attention"
+    type: str                      # "mamba2" | "parallel" | "retention" | "latent_attention" | "attention" | "channel_delta"
     ssd: SsdMixerConfig = None
     left: ChunkAttnConfig = None
     right: GlaConfig = None
@@ -304,6 +332,7 @@ class SeqLayerConfig:
     latent: LatentAttnConfig = None
     moe: MoeConfig = None          # routed feed-forward instead of the dense one
     attn: MaskedAttnConfig = None  # type "attention"
+    delta: DeltaConfig = None      # type "channel_delta"
     weights_of: int = -1           # >= 0: the layer owns no tensors and runs with that layer's (cache and state are its own)
 
 
@@ -316,6 +345,13 @@ SEQ_FAMILIES = {
     # positions, a gate per channel; two-matrix gelu feed-forward; softmax router, clamped gated experts
     "Dibedra": dict(block="parallel", norm_offset=0.0, positions=None, norm="dyt", dense="mlp", router="softmax", expert="clamp_glu",
                     attention=dict(rot_pairs=True, value_keys=True, gate="channel", sink=False)),
+    # sublayers read the residual stream itself (the mixer through a short convolution over time) and pass an RMS norm with ONE
+    # number as its weight on their way back into it; delta-rule, attention and latent-attention mixers; two-matrix gelu
+    # feed-forward; experts chosen by logit, weighted by the softmax over the chosen logits, gated silu experts
+    "Lugizen": dict(block="branchnorm", norm_offset=0.0, positions=None, norm_scalar=True, dense="mlp", router="topk_softmax",
+                    expert="silu_glu",
+                    attention=dict(rot_pairs=False, value_keys=False, gate="none", sink=False, unit_norm=True, temp=True),
+                    latent=dict(q_latent=True, gate=False, sink=False)),
 }
 
 
@@ -330,7 +366,10 @@ class SeqModelConfig:
     embed_scale: float = 1.0
     logit_softcap: float = 0.0
     eos_token_id: int = -1         # none unless config.json names one
-    block: str = "postnorm"        # "postnorm" | "prenorm_hc" (pre-norm sublayers on `streams` residual streams) | "parallel"
+    block: str = "postnorm"        # "postnorm" | "prenorm_hc" (pre-norm sublayers on `streams` residual streams) | "parallel" |
+                                   # "branchnorm" (x <- x + norm(sublayer(x)); the mixer reads x + conv(x) when canon_taps > 0)
+    canon_taps: int = 0            # taps of the causal convolution over time in front of every mixer (tensor l<i>.canon1 [width, taps])
+    norm_scalar: bool = False      # a norm's weight is ONE number (tensors of one element)
     norm: str = "rms"              # "rms" | "dyt" (tanh(alpha x) w + b; tensors <name>, <name>.b, <name>.alpha)
     dense: str = "glu"             # dense feed-forward: "glu" (gelu_tanh(gate) * up) | "mlp" (gelu_tanh(up))
     logit_scale: float = 1.0
@@ -381,7 +420,12 @@ class SeqModelConfig:
                 layers.append(SeqLayerConfig("attention", ff=ff, moe=moe, weights_of=-1 if share is None else share, attn=MaskedAttnConfig(
                     heads=int(mx["heads"]), kv_heads=int(mx.get("kv_heads", mx["heads"])), dim=int(mx["dim"]),
                     vdim=int(mx.get("vdim", mx["dim"])), window=int((mx.get("mask") or {}).get("size", 0)),
-                    scale=float(mx.get("scale", float(mx["dim"]) ** -0.5)), rot=rot, **fam["attention"])))
+                    scale=float(mx.get("scale", float(mx["dim"]) ** -0.5)), rot=rot, v_mix=bool(mx.get("v_mix", False)), **fam["attention"])))
+            elif L["type"] == "channel_delta":
+                layers.append(SeqLayerConfig("channel_delta", ff=ff, moe=moe, delta=DeltaConfig(
+                    heads=int(mx["heads"]), kv_heads=int(mx.get("kv_heads", mx["heads"])), dim=int(mx["dim"]),
+                    vdim=int(mx.get("vdim", mx["dim"])), conv=int(mx.get("conv", 4)), rank_a=int(mx.get("decay_rank", 0)),
+                    rank_g=int(mx.get("gate_rank", 0)))))
             elif L["type"] == "retention":
                 rot = RotaryConfig.from_json(mx["rot"]) if mx.get("rot") else RotaryConfig(0, 10000.0)
                 layers.append(SeqLayerConfig("retention", ff=ff, moe=moe, retention=RetentionConfig(
@@ -389,10 +433,12 @@ class SeqModelConfig:
                     decay=[float(x) for x in mx["decay"]], rot=rot)))
             elif L["type"] == "latent_attention":
                 src = mx.get("kv_from")
+                lf = fam.get("latent", {})
                 layers.append(SeqLayerConfig("latent_attention", ff=ff, moe=moe, latent=LatentAttnConfig(
                     heads=int(mx["heads"]), dim=int(mx["dim"]), rot_dim=int(mx["rot_dim"]), vdim=int(mx.get("vdim", mx["dim"])),
                     kv_rank=int(mx["kv_rank"]), scale=float(mx["scale"]), rot=RotaryConfig.from_json(mx["rot"], int(mx["rot_dim"])),
-                    kv_from=-1 if src is None else int(src))))
+                    kv_from=-1 if src is None else int(src), q_rank=int(mx.get("q_rank", 0)) if lf.get("q_latent") else 0,
+                    window=int((mx.get("mask") or {}).get("size", 0)), gate=lf.get("gate", True), sink=lf.get("sink", True))))
             elif L["type"] == "mamba2":
                 layers.append(SeqLayerConfig("mamba2", ssd=SsdMixerConfig(
                     heads=int(mx["heads"]), vdim=int(mx["vdim"]), state=int(mx["state"]), groups=int(mx.get("groups", 1)),
@@ -413,7 +459,8 @@ class SeqModelConfig:
             embed_scale=float((d.get("embedding") or {}).get("scale", 1.0)), logit_softcap=float(d.get("logit_softcap") or 0.0),
             eos_token_id=int(d.get("eos_token_id", -1)), block=fam["block"], streams=int(d.get("streams", 1)),
             norm_offset=fam["norm_offset"], positions=fam["positions"], norm=fam.get("norm", "rms"), dense=fam.get("dense", "glu"),
-            logit_scale=float(d.get("logit_scale", 1.0)))
+            logit_scale=float(d.get("logit_scale", 1.0)), canon_taps=int((d.get("canon") or {}).get("taps", 0)),
+            norm_scalar=bool(fam.get("norm_scalar", False)))
 
     def to_json(self) -> dict:
         """The inverse of from_json (used to write synthetic checkpoints)."""
@@ -430,11 +477,24 @@ class SeqModelConfig:
                 mx = dict(heads=a.heads, dim=a.dim, rot_dim=a.rot_dim, vdim=a.vdim, kv_rank=a.kv_rank, scale=a.scale, rot=a.rot.to_json())
                 if a.kv_from >= 0:
                     mx["kv_from"] = a.kv_from
+                if a.q_rank:
+                    mx["q_rank"] = a.q_rank
+                if a.window:
+                    mx["mask"] = dict(size=a.window)
             elif L.type == "attention":
                 a = L.attn
                 mx = dict(heads=a.heads, kv_heads=a.kv_heads, dim=a.dim, vdim=a.vdim, scale=a.scale, rot=a.rot.to_json())
                 if a.window:
                     mx["mask"] = dict(size=a.window)
+                if a.v_mix:
+                    mx["v_mix"] = True
+            elif L.type == "channel_delta":
+                t = L.delta
+                mx = dict(heads=t.heads, kv_heads=t.kv_heads, dim=t.dim, vdim=t.vdim, conv=t.conv)
+                if t.rank_a:
+                    mx["decay_rank"] = t.rank_a
+                if t.rank_g:
+                    mx["gate_rank"] = t.rank_g
             else:
                 l, r = L.left, L.right
                 mx = dict(left=dict(heads=l.heads, kv_heads=l.kv_heads, dim=l.dim, vdim=l.vdim, mask=dict(size=l.chunk), scale=l.scale),
@@ -447,6 +507,7 @@ class SeqModelConfig:
                     mlp["shared"] = dict(ff=e.shared_ff)
                 if e.act == "clamp_glu":
                     mlp["expert"]["limit"] = e.limit
+                if e.act != "relu2":
                     del mlp["router"]["scale"]
                 if e.identity:
                     mlp["router"]["identity"] = e.identity
@@ -455,6 +516,11 @@ class SeqModelConfig:
             out.append(dict(type=L.type, mixer=mx, mlp=mlp))
             if L.weights_of >= 0:
                 out[-1]["weights_of"] = L.weights_of
+        if self.block == "branchnorm":
+            out_d = dict(architecture=self.architecture, vocab=self.vocab, width=self.width, layers=out, norm=dict(eps=self.eps))
+            if self.canon_taps:
+                out_d["canon"] = dict(taps=self.canon_taps)
+            return out_d
         if self.block == "parallel":
             return dict(architecture=self.architecture, vocab=self.vocab, width=self.width, layers=out, norm=dict(eps=self.eps),
                         logit_scale=self.logit_scale)
@@ -469,6 +535,8 @@ class SeqModelConfig:
             raise ValueError("width and vocab must be positive")
         if self.block == "prenorm_hc" and not 1 <= self.streams <= 8:
             raise ValueError("1 to 8 residual streams")
+        if not 0 <= self.canon_taps <= 8 or (self.canon_taps and self.block != "branchnorm"):
+            raise ValueError("a convolution of 1 to 8 taps in front of the mixers is served in blocks normed on the sublayer's output")
         for i, L in enumerate(self.layers):
             if L.moe and not (1 <= L.moe.top <= L.moe.outputs <= 512 and L.moe.experts >= 1 and L.moe.identity >= 0):
                 raise ValueError(f"layer {i}: unsupported router sizes {L.moe}")
@@ -479,10 +547,21 @@ class SeqModelConfig:
                 raise ValueError(f"layer {i}: identity experts and a shared expert do not combine")
             if L.weights_of >= 0 and self.block != "parallel":
                 raise ValueError(f"layer {i}: shared layer weights are served in parallel blocks only")
+            if L.moe and L.moe.router == "topk_softmax" and (L.moe.identity or L.moe.groups or L.moe.shared_ff):
+                raise ValueError(f"layer {i}: weights over the chosen logits combine with neither identity experts, groups nor a shared expert")
+            if L.type == "channel_delta":
+                t = L.delta
+                if t.heads < 1 or t.kv_heads < 1 or t.heads % t.kv_heads or not 1 <= t.dim <= 512 or t.vdim < 1 or not 1 <= t.conv <= 8:
+                    raise ValueError(f"layer {i}: unsupported delta-rule sizes {t}")
+                continue
             if L.type == "attention":
                 a = L.attn
-                if self.block != "parallel":
-                    raise ValueError(f"layer {i}: the attention mixer is served in parallel blocks")
+                if self.block not in ("parallel", "branchnorm"):
+                    raise ValueError(f"layer {i}: the attention mixer is served in parallel blocks and in blocks normed on the sublayer's output")
+                if a.v_mix:
+                    first = next(x.attn for x in self.layers if x.type == "attention" and x.attn.v_mix)
+                    if a.value_keys or (first.kv_heads, first.vdim) != (a.kv_heads, a.vdim):
+                        raise ValueError(f"layer {i}: layers that mix values share the shape of their projected values")
                 if a.heads < 1 or a.kv_heads < 1 or a.heads % a.kv_heads or a.dim < 1 or a.window < 0 or a.rot.dims % 2 or \
                         a.rot.dims > a.dim or (a.value_keys and a.vdim != a.dim):
                     raise ValueError(f"layer {i}: unsupported attention sizes {a}")
@@ -500,6 +579,8 @@ class SeqModelConfig:
                 a = L.latent
                 if a.rot.dims != a.rot_dim or a.rot_dim % 2 or a.rot_dim < 2:
                     raise ValueError(f"layer {i}: the rotated part of a latent-attention head is rot_dim = rot.dims (even) channels")
+                if a.q_rank < 0 or a.window < 0:
+                    raise ValueError(f"layer {i}: unsupported latent-attention sizes {a}")
                 if a.kv_from >= 0:
                     o = self.layers[a.kv_from] if a.kv_from < i else None
                     if o is None or o.type != "latent_attention" or o.latent.kv_from >= 0 or \

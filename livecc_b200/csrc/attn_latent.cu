@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(256) latent_kv_append_kernel(const T* __restri
                                                                const float* __restrict__ inv_freq, float mag,
                                                                float* __restrict__ q_out, T* __restrict__ k_pages,
                                                                const int* __restrict__ page_table, int page_size, int H, int D,
-                                                               int DR, int R, SeqPos pos) {
+                                                               int DR, int R, SeqPos pos, const T* __restrict__ qsrc, int ld_q) {
     if (seq_done(pos)) return;
     __shared__ float red[32];
     const int t = blockIdx.x;
@@ -44,12 +44,12 @@ __global__ void __launch_bounds__(256) latent_kv_append_kernel(const T* __restri
         const int j = r < half ? r : r - half;
         const float ang = p * inv_freq[j];
         const float c = cosf(ang) * mag, s = sinf(ang) * mag;
-        const T* qr = row + (size_t)h * QH + D;
+        const T* qr = (qsrc ? qsrc + (size_t)t * ld_q : row) + (size_t)h * QH + D;
         const float v = ldf(qr + r), other = ldf(qr + (r < half ? r + half : r - half));
         q_out[((size_t)t * H + h) * KD + R + r] = r < half ? v * c - other * s : v * c + other * s;
     }
     if (!has_kv || blockIdx.y != 0) return;
-    const T* lat = row + nq;
+    const T* lat = qsrc ? row : row + nq;      // queries of their own: the row starts with the latent
     float ss = 0.f;
     for (int i = threadIdx.x; i < R; i += blockDim.x) { const float v = ldf(lat + i); ss = fmaf(v, v, ss); }
     ss = block_sum(ss, red);
@@ -69,17 +69,17 @@ __global__ void __launch_bounds__(256) latent_kv_append_kernel(const T* __restri
 
 int latent_kv_append(int dt, const void* proj, int ld, int has_kv, const float* norm_w, float eps, const float* inv_freq,
                      float mag, float* q_out, void* k_pages, const int* page_table, int page_size, int S, int H, int D,
-                     int DR, int R, SeqPos pos, cudaStream_t s) {
+                     int DR, int R, SeqPos pos, cudaStream_t s, const void* q, int ld_q) {
     if (!proj || !inv_freq || !q_out || S < 1 || H < 1 || D < 0 || DR < 2 || (DR & 1) || R < 1) return -2;
     if (has_kv && (!norm_w || !k_pages || !page_table || page_size < 1)) return -2;
     count_launch();
     const dim3 S_grid(S, S < 32 ? 4 : 1);
     if (dt == DT_F32)
         latent_kv_append_kernel<float><<<S_grid, 256, 0, s>>>((const float*)proj, ld, has_kv, norm_w, eps, inv_freq, mag, q_out,
-                                                         (float*)k_pages, page_table, page_size, H, D, DR, R, pos);
+                                                         (float*)k_pages, page_table, page_size, H, D, DR, R, pos, (const float*)q, ld_q);
     else
         latent_kv_append_kernel<bf16><<<S_grid, 256, 0, s>>>((const bf16*)proj, ld, has_kv, norm_w, eps, inv_freq, mag, q_out,
-                                                        (bf16*)k_pages, page_table, page_size, H, D, DR, R, pos);
+                                                        (bf16*)k_pages, page_table, page_size, H, D, DR, R, pos, (const bf16*)q, ld_q);
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }
 

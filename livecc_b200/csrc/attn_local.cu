@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(256) qk_headnorm_rope_append_kernel(const T* _
                                                                       int rot_dims, int rot_pairs, float* __restrict__ q_out,
                                                                       T* __restrict__ k_pages, T* __restrict__ v_pages,
                                                                       const int* __restrict__ page_table, int page_size, int S, int Hq,
-                                                                      int G, int D, int DV, SeqPos pos) {
+                                                                      int G, int D, int DV, SeqPos pos, AppendOpts ao) {
     if (seq_done(pos)) return;
     const int t = blockIdx.x;
     const int p = seq_past(pos, S) + t;
@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(256) qk_headnorm_rope_append_kernel(const T* _
             }
             for (int j = lane + 32 * kKeep; j < np; j += 32) { const float2 v = ld2(x + 2 * j); ss = fmaf(v.x, v.x, fmaf(v.y, v.y, ss)); }
             ss = warp_sum(ss);
-            const float rn = w ? 1.f / sqrtf(ss / (float)D + eps) : 1.f;
+            const float rn = ((w || ao.unit_norm) ? 1.f / sqrtf(ss / (float)D + eps) : 1.f) * ((is_q && ao.q_head_scale) ? ao.q_head_scale[hd] : 1.f);
             float* qo = q_out + ((size_t)t * Hq + hd) * D;
             T* ko = k_pages + (((size_t)page * G + (hd - Hq)) * page_size + slot) * D;
             auto emit = [&](int j, const float2 v) {
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(256) qk_headnorm_rope_append_kernel(const T* _
         }
         for (int c = lane; c < D; c += 32) { const float v = ldf(x + c); ss = fmaf(v, v, ss); }
         ss = warp_sum(ss);
-        const float rn = w ? 1.f / sqrtf(ss / (float)D + eps) : 1.f;
+        const float rn = ((w || ao.unit_norm) ? 1.f / sqrtf(ss / (float)D + eps) : 1.f) * ((is_q && ao.q_head_scale) ? ao.q_head_scale[hd] : 1.f);
         for (int c = lane; c < D; c += 32) {
             float v = ldf(x + c) * rn * (w ? w[c] : 1.f);
             if (c < rot_dims) {
@@ -133,7 +133,10 @@ __global__ void __launch_bounds__(256) qk_headnorm_rope_append_kernel(const T* _
     const int nv = G * DV;
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < nv; i += gridDim.y * blockDim.x) {
         const int g = i / DV, d = i % DV;
-        v_pages[(((size_t)page * G + g) * page_size + slot) * DV + d] = row[v_col + i];
+        T* dst = v_pages + (((size_t)page * G + g) * page_size + slot) * DV + d;
+        if (ao.v_keep) ((T*)ao.v_keep)[(size_t)t * ao.ld_keep + i] = row[v_col + i];
+        if (ao.v_mix) stf(dst, fmaf(ao.mix, ldf((const T*)ao.v_mix + (size_t)t * ao.ld_mix + i), (1.f - ao.mix) * ldf(row + v_col + i)));
+        else *dst = row[v_col + i];
     }
 }
 
@@ -945,10 +948,12 @@ int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_p
 int qk_headnorm_rope_append(int dt, const void* proj, int ld, int v_col, const float* qn_w, const float* kn_w, float eps,
                             const float* inv_freq, float mag, int rot_dims, int rot_pairs, float* q_out, void* k_pages,
                             void* v_pages, const int* page_table, int page_size, int S, int Hq, int G, int D, int DV, SeqPos pos,
-                            cudaStream_t s) {
+                            cudaStream_t s, const AppendOpts* opt) {
     if (!proj || !q_out || !k_pages || !v_pages || !page_table || S < 1 || Hq < 1 || G < 1 || D < 1 || DV < 1 || page_size < 1 ||
         rot_dims < 0 || (rot_dims & 1) || rot_dims > D || (rot_dims > 0 && !inv_freq) || v_col < 0 || v_col + G * DV > ld)
         return -2;
+    const AppendOpts ao = opt ? *opt : AppendOpts{false, nullptr, nullptr, 0, 0.f, nullptr, 0};
+    if ((ao.v_mix && ao.ld_mix < G * DV) || (ao.v_keep && ao.ld_keep < G * DV)) return -2;
     count_launch();
     // many rows: 8 warps walk a row's heads; few rows: 4-warp CTAs, one head per warp, so that a decode step fills more SMs
     const int threads = S >= 64 ? 256 : 128;
@@ -959,7 +964,7 @@ int qk_headnorm_rope_append(int dt, const void* proj, int ld, int v_col, const f
 #define LCC_APPEND(T, P)                                                                                                      \
     qk_headnorm_rope_append_kernel<T, P><<<grid, threads, 0, s>>>((const T*)proj, ld, v_col, qn_w, kn_w, eps, inv_freq, mag, rot_dims,  \
                                                                   rot_pairs, q_out, (T*)k_pages, (T*)v_pages, page_table, page_size, S, Hq, \
-                                                                  G, D, DV, pos)
+                                                                  G, D, DV, pos, ao)
     if (dt == DT_F32) { if (pairs) LCC_APPEND(float, true); else LCC_APPEND(float, false); }
     else { if (pairs) LCC_APPEND(bf16, true); else LCC_APPEND(bf16, false); }
 #undef LCC_APPEND

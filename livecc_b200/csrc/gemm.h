@@ -19,7 +19,8 @@ enum GemmEpilogue {
     EPI_RELU2 = 8,           // C = bf16(relu(acc)^2)
     EPI_GELU_TANH = 9,       // C = bf16(gelu_tanh(acc)), the activation in fp32 on the accumulator
     EPI_CLAMP_GLU = 10,      // gate/up rows interleaved by 16 as for EPI_SWIGLU: g = min(gate, limit), u = clamp(up, +-limit),
-                             // C[:, j] = bf16(g * sigmoid(1.702 g) * (u + 1)) in fp32 on the accumulators; limit = epi_param
+                             // C[:, j] = bf16(g * sigmoid(alpha g) * (u + up_bias)) in fp32 on the accumulators; limit = epi_param,
+                             // alpha = epi_alpha, up_bias = epi_up_bias (1, 0 and an infinite limit: silu(gate) * up)
 };
 
 struct GemmArgs {
@@ -50,6 +51,7 @@ struct GemmArgs {
     // fp32 output: C is float [M, ldc] (ldc a multiple of 4), epi must be EPI_NONE
     bool c_f32 = false;
     float epi_param = 0.f;   // EPI_CLAMP_GLU: the clamp
+    float epi_alpha = 1.702f, epi_up_bias = 1.f;
 };
 
 int gemm_bf16_tn(const GemmArgs& a, int num_sms, cudaStream_t stream);

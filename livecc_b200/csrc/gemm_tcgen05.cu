@@ -102,9 +102,12 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&v)[32], bf16* C,
         }
     } else if (EPI == EPI_CLAMP_GLU) {
         // the same 32-row interleave; the activation runs in fp32 on the accumulators and is rounded once. The clamp rides in
-        // the (otherwise unused) residual stride as float bits.
+        // the (otherwise unused) residual stride as float bits, the sigmoid's slope and the offset of the up half in the
+        // (otherwise unused) bias pointer's bits.
         if (row_ok && col0 < tile_end) {
             const float limit = __int_as_float(ldr);
+            const unsigned long long pb = (unsigned long long)bias;
+            const float alpha = __uint_as_float((unsigned)(pb & 0xffffffffull)), up_bias = __uint_as_float((unsigned)(pb >> 32));
             const int ocol0 = (col0 >> 5) << 4;
             uint32_t o[8];
 #pragma unroll
@@ -114,7 +117,7 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&v)[32], bf16* C,
                 for (int e = 0; e < 2; ++e) {
                     const float g = fminf(__uint_as_float(v[2 * j + e]), limit);
                     const float u = fminf(fmaxf(__uint_as_float(v[16 + 2 * j + e]), -limit), limit);
-                    y[e] = g / (1.f + __expf(-1.702f * g)) * (u + 1.f);
+                    y[e] = g / (1.f + __expf(-alpha * g)) * (u + up_bias);
                 }
                 o[j] = pack_bf16x2(y[0], y[1]);
             }
@@ -581,9 +584,15 @@ static int launch_cfg(const GemmArgs& a, int bn, int num_sms, cudaStream_t strea
     const int grid = tiles < num_sms ? tiles : num_sms;
     lcc::count_launch();
     int ldr = a.ldr;
-    if (EPI == EPI_CLAMP_GLU) memcpy(&ldr, &a.epi_param, sizeof(int));   // no residual in this epilogue: the slot carries the clamp
+    const bf16* bias = (const bf16*)a.bias;
+    if (EPI == EPI_CLAMP_GLU) {   // no residual and no bias in this epilogue: the slots carry the clamp, the slope and the offset
+        memcpy(&ldr, &a.epi_param, sizeof(int));
+        const float ab[2] = {a.epi_alpha, a.epi_up_bias};
+        static_assert(sizeof(bias) == sizeof(ab), "two floats ride in a pointer");
+        memcpy(&bias, ab, sizeof(ab));
+    }
     kern<<<grid, 384, cfg.smem_bytes, stream>>>(ta, tb, (bf16*)a.C, a.M, a.N, a.K, a.ldc,
-                                                (const bf16*)a.bias, (const bf16*)a.residual,
+                                                bias, (const bf16*)a.residual,
                                                 ldr, splits, cfg, a.tile_group, batch, a.a_col_stride, a.c_col_stride);
     return cudaGetLastError() == cudaSuccess ? 0 : -13;
 }

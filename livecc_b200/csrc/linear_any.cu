@@ -30,6 +30,7 @@ struct Grp {
     int glu_F;     // few-row kernel, GLU form: a warp owns output column n = the gate row and the up row of that column
     int glu_il16;
     float glu_limit;
+    float glu_alpha, glu_up_bias;   // g * sigmoid(alpha g) * (u + up_bias)
 };
 __device__ __forceinline__ float act_of(float v, int act) {
     if (act == ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
@@ -206,7 +207,7 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const T* __restrict__ 
             if (m < M) {
                 const float gt = fminf(warp_sum(acc[0][m]), g.glu_limit);
                 const float up = fminf(fmaxf(warp_sum(acc[WR - 1][m]), -g.glu_limit), g.glu_limit);
-                if (lane == 0) stf(C + (size_t)m * ldc + n0, gt / (1.f + expf(-1.702f * gt)) * (up + 1.f));
+                if (lane == 0) stf(C + (size_t)m * ldc + n0, gt / (1.f + expf(-g.glu_alpha * gt)) * (up + g.glu_up_bias));
             }
         }
         continue;
@@ -267,7 +268,7 @@ int launch_linear(const void* A, int lda, const void* W, int ldw, const float* b
         linear_tile_kernel<T, T><<<grid, 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, bias, (T*)glu_tmp, ld_tmp, M, 2 * N, K, raw);
         if (cudaGetLastError() != cudaSuccess) return -100;
         const int rows = g.row_off ? M_total : M;
-        return glu_clamp_swish(sizeof(T) == 4 ? DT_F32 : DT_BF16, glu_tmp, ld_tmp, C, ldc, rows, N, g.glu_limit, s, g.glu_il16 != 0);
+        return glu_clamp_swish(sizeof(T) == 4 ? DT_F32 : DT_BF16, glu_tmp, ld_tmp, C, ldc, rows, N, g.glu_limit, s, g.glu_il16 != 0, g.glu_alpha, g.glu_up_bias);
     } else {
         dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, groups);
         count_launch();
@@ -293,7 +294,7 @@ int linear_grouped(const GroupedLinear& q, cudaStream_t s) {
     if (q.glu_F > 0 && (q.N != q.glu_F || q.act != ACT_NONE || q.c_f32 || (q.glu_il16 && (q.glu_F % 16)) || q.c_stride != 0 ||
                         (q.groups > 1 && !q.row_off)))
         return -2;
-    const Grp g{q.a_stride, q.w_stride, q.c_stride, q.row_off, q.a_rows, q.act, 0, q.glu_F, q.glu_il16 ? 1 : 0, q.glu_limit};
+    const Grp g{q.a_stride, q.w_stride, q.c_stride, q.row_off, q.a_rows, q.act, 0, q.glu_F, q.glu_il16 ? 1 : 0, q.glu_limit, q.glu_alpha, q.glu_up_bias};
     const int mt = q.row_off ? (q.M_total > 0 ? q.M_total : q.M * q.groups) : 0;
     if (q.dt == DT_F32) return launch_linear<float, float>(q.A, q.lda, q.W, q.ldw, nullptr, q.C, q.ldc, q.M, q.N, q.K, s, q.groups, g, mt, q.glu_tmp, q.ld_tmp);
     if (q.c_f32) return launch_linear<bf16, float>(q.A, q.lda, q.W, q.ldw, nullptr, q.C, q.ldc, q.M, q.N, q.K, s, q.groups, g, mt);

@@ -51,8 +51,8 @@ __device__ __forceinline__ void route_row(const float* __restrict__ z, const flo
 #pragma unroll
     for (int i = 0; i < kMaxExpertsPerLane; ++i) {
         const int e = lane + 32 * i;
-        sc[i] = e < E ? (ro.softmax ? sc[i] * zsum : sigmoid_f(z[e])) : 0.f;
-        ch[i] = e < E ? sc[i] + correction[e] : -INFINITY;
+        sc[i] = e < E ? (ro.topk_softmax ? z[e] : (ro.softmax ? sc[i] * zsum : sigmoid_f(z[e]))) : 0.f;
+        ch[i] = e < E ? sc[i] + (correction ? correction[e] : 0.f) : -INFINITY;
     }
     if (ro.groups > 0) {
         const int per = E / ro.groups;
@@ -107,6 +107,16 @@ __device__ __forceinline__ void route_row(const float* __restrict__ z, const flo
     }
 }
 
+// ro.topk_softmax: route_row emitted the chosen logits in descending order of choice; one lane turns a row's `top` logits into the
+// softmax over them (times scale) in place.
+__device__ __forceinline__ void softmax_chosen(float* w, int top, float scale) {
+    float m = -INFINITY, sum = 0.f;
+    for (int k = 0; k < top; ++k) m = fmaxf(m, w[k]);
+    for (int k = 0; k < top; ++k) { w[k] = expf(w[k] - m); sum += w[k]; }
+    const float inv = scale / sum;
+    for (int k = 0; k < top; ++k) w[k] *= inv;
+}
+
 constexpr int kRouteScratch = 32 * kMaxExpertsPerLane;   // per warp: choice scores of a row, flags of the kept groups
 
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ correction,
@@ -123,10 +133,11 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     float idw = 0.f;         // lane 0: the weights of the chosen identity experts
     route_row(z, correction, E, top, ro, gch[warp], gkeep[warp], [&](int k, int be, float bs) {
         sel[(size_t)r * top + k] = be;
-        weight[(size_t)r * top + k] = bs * scale;
+        weight[(size_t)r * top + k] = ro.topk_softmax ? bs : bs * scale;
         if (be < real) rank[(size_t)r * top + k] = atomicAdd(counts + be, 1);
         else { rank[(size_t)r * top + k] = -1; idw += bs * scale; }
     });
+    if (ro.topk_softmax && lane == 0) softmax_chosen(weight + (size_t)r * top, top, scale);
     if (shared_gate && lane == 0) shared_gate[r] = ro.identity > 0 ? idw : sigmoid_f(z[E]);
 }
 
@@ -151,10 +162,11 @@ __global__ void __launch_bounds__(256) moe_route_small_kernel(const float* __res
         float idw = 0.f;
         route_row(z, correction, E, top, ro, gch[warp], gkeep[warp], [&](int k, int be, float bs) {
             sel[(size_t)r * top + k] = be;
-            weight[(size_t)r * top + k] = bs * scale;
+            weight[(size_t)r * top + k] = ro.topk_softmax ? bs : bs * scale;
             if (be < real) rk[r * top + k] = atomicAdd(&cnt[be], 1);
             else { rk[r * top + k] = -1; idw += bs * scale; }
         });
+        if (ro.topk_softmax && lane == 0) softmax_chosen(weight + (size_t)r * top, top, scale);
         if (shared_gate && lane == 0) shared_gate[r] = ro.identity > 0 ? idw : sigmoid_f(z[E]);
     }
     __syncthreads();
@@ -234,13 +246,14 @@ __global__ void moe_combine_kernel(const T* __restrict__ eo, int ld_eo, const in
 static bool router_ok(const MoeRouterOpts& ro, int E, int top, const float* shared_gate) {
     if (ro.identity < 0 || ro.identity >= E || (ro.identity > 0 && !shared_gate)) return false;
     if (ro.groups > 0 && (E % ro.groups || ro.keep < 1 || ro.keep > ro.groups || ro.keep * (E / ro.groups) < top)) return false;
+    if (ro.topk_softmax && (ro.identity > 0 || ro.groups > 0 || ro.softmax)) return false;
     return ro.groups >= 0;
 }
 
 int moe_route(const float* logits, int ld, const float* correction, int E, int top, float scale, int* sel, float* weight,
               float* shared_gate, int* counts, int* rank, int S, cudaStream_t s, const MoeRouterOpts* opt) {
     const MoeRouterOpts ro = opt ? *opt : MoeRouterOpts{false, 0, 0, 0};
-    if (!logits || !correction || !sel || !weight || !counts || !rank || S < 1 || E < 1 || E > 32 * kMaxExpertsPerLane || top < 1 ||
+    if (!logits || !sel || !weight || !counts || !rank || S < 1 || E < 1 || E > 32 * kMaxExpertsPerLane || top < 1 ||
         top > E || ld < E + ((shared_gate && !ro.identity) ? 1 : 0) || !router_ok(ro, E, top, shared_gate))
         return -2;
     count_launch();
@@ -251,7 +264,7 @@ int moe_route(const float* logits, int ld, const float* correction, int E, int t
 int moe_route_small(const float* logits, int ld, const float* correction, int E, int top, float scale, int* sel, float* weight,
                     float* shared_gate, int* row_off, int* pos, int* src_row, int S, cudaStream_t s, const MoeRouterOpts* opt) {
     const MoeRouterOpts ro = opt ? *opt : MoeRouterOpts{false, 0, 0, 0};
-    if (!logits || !correction || !sel || !weight || !row_off || !pos || !src_row || S < 1 || E < 1 || E > kSmallRouteExperts ||
+    if (!logits || !sel || !weight || !row_off || !pos || !src_row || S < 1 || E < 1 || E > kSmallRouteExperts ||
         top < 1 || top > E || S * top > kSmallRouteItems || ld < E + ((shared_gate && !ro.identity) ? 1 : 0) || !router_ok(ro, E, top, shared_gate))
         return -2;
     count_launch();

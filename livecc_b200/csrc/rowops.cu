@@ -19,6 +19,7 @@ template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = _
 __device__ __forceinline__ int seq_past(const SeqPos& p, int) { return p.kv_len ? *p.kv_len : p.past; }
 __device__ __forceinline__ bool seq_done(const SeqPos& p) { return p.finished && *p.finished; }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 
 template <typename T>
 __global__ void embed_sinusoid_kernel(const int64_t* __restrict__ ids, const int* __restrict__ seq_len, const T* __restrict__ table,
@@ -152,13 +153,13 @@ __global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* __re
         }
 #pragma unroll
         for (int i = 0; i < EN; ++i) {
-            vg[i] = silu_f(vg[i]);
-            const float v = gate_first ? vy[i] * vg[i] : vy[i];
+            vg[i] = gate_first == 2 ? sigmoid_f(vg[i]) : silu_f(vg[i]);
+            const float v = gate_first == 1 ? vy[i] * vg[i] : vy[i];
             ss = fmaf(v, v, ss);
         }
     } else {
         for (int c = lane; c < group; c += TEAM) {
-            const float v = gate_first ? yr[c] * silu_f(ldf(gr + c)) : yr[c];
+            const float v = gate_first == 1 ? yr[c] * silu_f(ldf(gr + c)) : yr[c];
             ss = fmaf(v, v, ss);
         }
     }
@@ -171,15 +172,15 @@ __global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* __re
             if (c < group) {
                 const int wi = wb + c;
                 const float wv = w[wi < w_len ? wi : wi % w_len];
-                stf(out + (size_t)r * ld_out + c0 + c, gate_first ? vy[i] * vg[i] * rn * wv : vy[i] * rn * wv * vg[i]);
+                stf(out + (size_t)r * ld_out + c0 + c, gate_first == 1 ? vy[i] * vg[i] * rn * wv : vy[i] * rn * wv * vg[i]);
             }
         }
     } else {
         for (int c = lane; c < group; c += TEAM) {
-            const float gsl = silu_f(ldf(gr + c));
+            const float gsl = gate_first == 2 ? sigmoid_f(ldf(gr + c)) : silu_f(ldf(gr + c));
             const int wi = wb + c;
             const float wv = w[wi < w_len ? wi : wi % w_len];
-            const float v = gate_first ? yr[c] * gsl * rn * wv : yr[c] * rn * wv * gsl;
+            const float v = gate_first == 1 ? yr[c] * gsl * rn * wv : yr[c] * rn * wv * gsl;
             stf(out + (size_t)r * ld_out + c0 + c, v);
         }
     }
@@ -206,6 +207,19 @@ __global__ void __launch_bounds__(256) gather_rmsnorm_kernel(const float* __rest
     ss = block_sum(ss, red);
     const float rn = 1.f / sqrtf(ss / (float)W + eps);
     for (int c = threadIdx.x; c < W; c += blockDim.x) stf(out + (size_t)i * W + c, x[c] * rn * w[c]);
+}
+
+// out[r, :n] = rms(in[r, :n]) * w: one CTA per row of a slice in the storage type
+template <typename T>
+__global__ void __launch_bounds__(128) slice_rmsnorm_kernel(const T* __restrict__ in, int ld_in, const float* __restrict__ w, float eps,
+                                                            T* __restrict__ out, int ld_out, int n) {
+    __shared__ float red[32];
+    const T* x = in + (size_t)blockIdx.x * ld_in;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) { const float v = ldf(x + c); ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, red);
+    const float rn = 1.f / sqrtf(ss / (float)n + eps);
+    for (int c = threadIdx.x; c < n; c += blockDim.x) stf(out + (size_t)blockIdx.x * ld_out + c, ldf(x + c) * rn * w[c]);
 }
 
 __global__ void softcap_kernel(float* __restrict__ x, int64_t n, float cap, float inv_cap, float scale) {
@@ -335,14 +349,83 @@ __global__ void __launch_bounds__(256) residual_norm_kernel(float* __restrict__ 
 }
 
 template <typename T>
-__global__ void glu_clamp_swish_kernel(const T* __restrict__ gu, int ld, T* __restrict__ out, int ld_out, int S, int F, float limit, bool il16) {
+__global__ void glu_clamp_swish_kernel(const T* __restrict__ gu, int ld, T* __restrict__ out, int ld_out, int S, int F, float limit, bool il16,
+                                       float alpha, float up_bias) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (int64_t)S * F) return;
     const int r = (int)(i / F), c = (int)(i % F);
     const int gc = il16 ? ((c >> 4) << 5) + (c & 15) : c, uc = il16 ? gc + 16 : F + c;
     const float g = fminf(ldf(gu + (size_t)r * ld + gc), limit);
     const float u = fminf(fmaxf(ldf(gu + (size_t)r * ld + uc), -limit), limit);
-    stf(out + (size_t)r * ld_out + c, g / (1.f + expf(-1.702f * g)) * (u + 1.f));
+    stf(out + (size_t)r * ld_out + c, g / (1.f + expf(-alpha * g)) * (u + up_bias));
+}
+
+// x <- x + rms(y) * w for one row per CTA, y = the sublayer's row or the routed feed-forward's weighted sum of expert rows. A
+// thread keeps its E columns of y in registers between the sum of squares and the update (E = 0: rows wider than 256 * 16
+// columns form y twice). Each column's sum runs in the same order for every S.
+template <typename T, int E>
+__global__ void __launch_bounds__(256) branch_norm_residual_kernel(float* __restrict__ x32, const T* __restrict__ a, int ld_a, bool has_mc,
+                                                                   MoeCombine mc, const float* __restrict__ w, float eps,
+                                                                   T* __restrict__ xa, int W) {
+    __shared__ float red[32];
+    __shared__ int spos[kCombineTop];
+    __shared__ float swt[kCombineTop];
+    const int r = blockIdx.x;
+    float* x = x32 + (size_t)r * W;
+    const int top = has_mc ? mc.top : 0;
+    const bool cached = top <= kCombineTop;
+    if (has_mc && cached) {
+        if (threadIdx.x < top) {
+            spos[threadIdx.x] = mc.pos[(size_t)r * top + threadIdx.x];
+            swt[threadIdx.x] = mc.weight[(size_t)r * top + threadIdx.x];
+        }
+        __syncthreads();
+    }
+    const float gs = (has_mc && mc.so) ? mc.gate[r] : 0.f;
+    auto value = [&](int c) -> float {
+        if (!has_mc) return ldf(a + (size_t)r * ld_a + c);
+        float y = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int p = cached ? spos[k] : mc.pos[(size_t)r * top + k];
+            if (p < 0) continue;
+            const float wk = cached ? swt[k] : mc.weight[(size_t)r * top + k];
+            y = fmaf(wk, ldf((const T*)mc.eo + (size_t)p * mc.ld_eo + c), y);
+        }
+        if (mc.so) y = fmaf(gs, ldf((const T*)mc.so + (size_t)r * mc.ld_so + c), y);
+        return y;
+    };
+    constexpr int EN = E > 0 ? E : 1;
+    float vy[EN];
+    float ss = 0.f;
+    if (E > 0) {
+#pragma unroll
+        for (int i = 0; i < EN; ++i) {
+            const int c = threadIdx.x + i * 256;
+            vy[i] = c < W ? value(c) : 0.f;
+            ss = fmaf(vy[i], vy[i], ss);
+        }
+    } else {
+        for (int c = threadIdx.x; c < W; c += 256) { const float y = value(c); ss = fmaf(y, y, ss); }
+    }
+    ss = block_sum(ss, red);
+    const float rn = 1.f / sqrtf(ss / (float)W + eps);
+    if (E > 0) {
+#pragma unroll
+        for (int i = 0; i < EN; ++i) {
+            const int c = threadIdx.x + i * 256;
+            if (c < W) {
+                const float v = fmaf(vy[i] * rn, w[c], x[c]);
+                x[c] = v;
+                if (xa) stf(xa + (size_t)r * W + c, v);
+            }
+        }
+    } else {
+        for (int c = threadIdx.x; c < W; c += 256) {
+            const float v = fmaf(value(c) * rn, w[c], x[c]);
+            x[c] = v;
+            if (xa) stf(xa + (size_t)r * W + c, v);
+        }
+    }
 }
 
 inline int done() { return cudaGetLastError() == cudaSuccess ? 0 : -100; }
@@ -433,6 +516,16 @@ int gather_rmsnorm(int dt, const float* x32, const int* rows, const float* w, fl
     return done();
 }
 
+int slice_rmsnorm(int dt, const void* in, int ld_in, const float* w, float eps, void* out, int ld_out, int S, int n, cudaStream_t s) {
+    if (!in || !w || !out || S < 1 || n < 1 || ld_in < n || ld_out < n) return -2;
+    count_launch();
+    if (dt == DT_F32)
+        slice_rmsnorm_kernel<float><<<S, 128, 0, s>>>((const float*)in, ld_in, w, eps, (float*)out, ld_out, n);
+    else
+        slice_rmsnorm_kernel<bf16><<<S, 128, 0, s>>>((const bf16*)in, ld_in, w, eps, (bf16*)out, ld_out, n);
+    return done();
+}
+
 int softcap(float* x, int64_t n, float cap, cudaStream_t s, float scale) {
     if (!x || n < 1) return -2;
     if (!(cap > 0.f) && scale == 1.f) return 0;
@@ -473,14 +566,37 @@ int residual_norm(int dt, float* x32, const void* a, int ld_a, const void* b, in
     return done();
 }
 
-int glu_clamp_swish(int dt, const void* gu, int ld, void* out, int ld_out, int S, int F, float limit, cudaStream_t s, bool il16) {
+int branch_norm_residual(int dt, float* x32, const void* a, int ld_a, const MoeCombine* mc, const float* w, float eps, void* xa,
+                         int S, int W, cudaStream_t s) {
+    if (!x32 || !w || S < 1 || W < 1 || (!a && !mc) || (a && mc)) return -2;
+    if (mc && (!mc->eo || !mc->pos || !mc->weight || mc->top < 1 || (mc->so && !mc->gate))) return -2;
+    count_launch();
+    const MoeCombine m = mc ? *mc : MoeCombine{};
+#define LCC_BNR(E)                                                                                                             \
+    do {                                                                                                                       \
+        if (dt == DT_F32) branch_norm_residual_kernel<float, E><<<S, 256, 0, s>>>(x32, (const float*)a, ld_a, mc != nullptr, m, w, eps, (float*)xa, W); \
+        else branch_norm_residual_kernel<bf16, E><<<S, 256, 0, s>>>(x32, (const bf16*)a, ld_a, mc != nullptr, m, w, eps, (bf16*)xa, W);                 \
+    } while (0)
+    const int per = (W + 255) / 256;
+    if (per <= 1) LCC_BNR(1);
+    else if (per <= 2) LCC_BNR(2);
+    else if (per <= 4) LCC_BNR(4);
+    else if (per <= 8) LCC_BNR(8);
+    else if (per <= kRowCache) LCC_BNR(16);
+    else LCC_BNR(0);
+#undef LCC_BNR
+    return done();
+}
+
+int glu_clamp_swish(int dt, const void* gu, int ld, void* out, int ld_out, int S, int F, float limit, cudaStream_t s, bool il16,
+                    float alpha, float up_bias) {
     if (!gu || !out || S < 1 || F < 1 || (il16 && (F % 16))) return -2;
     const int64_t n = (int64_t)S * F;
     count_launch();
     if (dt == DT_F32)
-        glu_clamp_swish_kernel<float><<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const float*)gu, ld, (float*)out, ld_out, S, F, limit, il16);
+        glu_clamp_swish_kernel<float><<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const float*)gu, ld, (float*)out, ld_out, S, F, limit, il16, alpha, up_bias);
     else
-        glu_clamp_swish_kernel<bf16><<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const bf16*)gu, ld, (bf16*)out, ld_out, S, F, limit, il16);
+        glu_clamp_swish_kernel<bf16><<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const bf16*)gu, ld, (bf16*)out, ld_out, S, F, limit, il16, alpha, up_bias);
     return done();
 }
 

@@ -2,8 +2,9 @@
 // decode token per sequence) over every layer and produces the logits of the wanted rows. Prefill and decode use the
 // same launch sequence; what differs is the row count and which kernel of an op the shape selects.
 // A layer is a mixer (its output lands in one buffer), a feed-forward (dense or routed) and the block form around them
-// (post-norm residual, pre-norm sublayers on several residual streams, or a parallel block whose mixer and feed-forward read
-// one normed row); the three are chosen independently per model.
+// (post-norm residual, pre-norm sublayers on several residual streams, a parallel block whose mixer and feed-forward read
+// one normed row, or sublayers that read the residual stream itself and are normed on their way back into it); the three are
+// chosen independently per model.
 // The host (Python) owns every buffer; this file only sequences kernel launches.
 #include <stdlib.h>
 #include <string.h>
@@ -44,6 +45,10 @@ struct Dims {
                                                         // gate column, absorbed-output columns, value columns
     int m_nq, m_nk, m_nv, m_vcol, m_gate, m_ngate, m_proj, m_o;   // masked attention: q, k, projected v columns, the values' first column,
                                                                   // the gate's first column and width, projection rows, output columns
+    int a_qin;                                   // latent attention: the projection's leading query block (the heads, or their latent)
+    int d_nk, d_nv, d_k, d_v, d_conv_ch, d_b, d_a1, d_g1, d_proj;   // delta rule: q / k columns, v columns, first columns of k, v, beta,
+                                                                    // decay bottleneck, gate bottleneck (every block starts at a multiple of
+                                                                    // 8 columns; q, k, v and their padding are the convolution's channels)
 };
 Dims dims_of(const lcc_seq_layer& L) {
     Dims z{};
@@ -65,8 +70,9 @@ Dims dims_of(const lcc_seq_layer& L) {
         z.a_nq = L.a_heads * (L.a_dim + L.a_rot_dim);
         z.a_kd = L.a_rank + L.a_rot_dim;
         z.a_kv = L.a_kv_from >= 0 ? 0 : z.a_kd;
-        z.a_gate = z.a_nq + z.a_kv;
-        z.a_proj = z.a_gate + L.a_heads;
+        z.a_qin = L.a_q_rank > 0 ? L.a_q_rank : z.a_nq;
+        z.a_gate = z.a_qin + z.a_kv;
+        z.a_proj = z.a_gate + (L.a_gate ? L.a_heads : 0);
         z.a_lat = L.a_heads * L.a_rank;
         z.a_o = L.a_heads * L.a_vdim;
     } else if (L.type == LCC_MIX_ATTENTION) {
@@ -77,6 +83,12 @@ Dims dims_of(const lcc_seq_layer& L) {
         z.m_ngate = L.m_gate == LCC_GATE_CHANNEL ? L.m_heads * L.m_vdim : (L.m_gate == LCC_GATE_HEAD ? L.m_heads : 0);
         z.m_proj = z.m_gate + z.m_ngate;
         z.m_o = L.m_heads * L.m_vdim;
+    } else if (L.type == LCC_MIX_DELTA) {
+        auto up8 = [](int n) { return (n + 7) / 8 * 8; };
+        z.d_nk = L.d_kv_heads * L.d_dim; z.d_nv = L.d_heads * L.d_vdim;
+        z.d_k = up8(z.d_nk); z.d_v = z.d_k + up8(z.d_nk); z.d_conv_ch = z.d_v + up8(z.d_nv);
+        z.d_b = z.d_conv_ch; z.d_a1 = z.d_b + up8(L.d_heads); z.d_g1 = z.d_a1 + up8(L.d_rank_a);
+        z.d_proj = z.d_g1 + up8(L.d_rank_g);
     }
     return z;
 }
@@ -90,10 +102,11 @@ constexpr int kMoeTcMinRows = 256;   // routed rows (tokens x top) from which th
 constexpr int kForkMaxRows = 32;     // rows up to which the shared expert runs on the second stream
 
 struct WsLayout {
-    size_t x32, xa, proj, proj2, mid, mid2, y32, q32, f1, f2, o1, o2, xf, scan, scan_floats, xsum, moe_f, moe_i, moe_x, moe_h, moe_g, moe_o, split, split_floats, total;
+    size_t x32, xa, proj, proj2, mid, mid2, y32, q32, f1, f2, o1, o2, xf, vkeep, scan, scan_floats, xsum, moe_f, moe_i, moe_x, moe_h, moe_g, moe_o, split, split_floats, total;
     int moe_rows;         // rows of the expert-sorted buffers: top per token, every list padded to a whole 128-row tile
     int w_proj, w_proj2, w_mid, w_y, w_q, w_f;
     int moe_e, moe_top;   // largest expert count and top-k of any layer (0: no routed feed-forward)
+    int w_vkeep;          // widest value row that a layer keeps for later layers of the step (0: none)
 };
 
 WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
@@ -104,8 +117,15 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
     size_t scan_floats = 0;
     int moe_e = 0, moe_top = 0, moe_ff = 0, moe_rows = 0, moe_glu = 0;   // moe_glu: widest hidden row of a gated expert
     size_t split_floats = 0;   // key-split partials of few-row plain causal attention
+    int wvk = 0;
     for (const lcc_seq_layer& l : m->layers) {
         const Dims z = dims_of(l);
+        if (l.type == LCC_MIX_DELTA) {
+            wp = std::max(wp, z.d_proj); wm = std::max(wm, std::max(z.d_conv_ch, ld8(z.d_nv))); wp2 = std::max(wp2, ld8(z.d_nv));
+            wy = std::max(wy, z.d_nv); wf = std::max(wf, l.d_heads * l.d_dim);
+        }
+        if (l.type == LCC_MIX_LATENT && l.a_q_rank > 0) { wp2 = std::max(wp2, ld8(z.a_nq)); wm = std::max(wm, ld8(l.a_q_rank)); }
+        if (l.type == LCC_MIX_ATTENTION && l.m_vmix_role == 1) wvk = std::max(wvk, ld8(z.m_nv));
         if (l.type == LCC_MIX_SSD) {
             wp = std::max(wp, ld8(z.s_proj)); wm = std::max(wm, ld8(std::max(z.conv_ch, z.inner)));
             wy = std::max(wy, z.inner); wf = std::max(wf, l.s_heads);
@@ -132,7 +152,7 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
                 split_floats = std::max(split_floats, lcc::attn_split_ws_floats(lcc::kAttnTiledMin - 1, l.m_heads, l.m_vdim));
         }
         if (l.ff_kind == LCC_FF_MOE) {
-            const bool glu = l.e_act == LCC_EXPERT_CLAMP_GLU;
+            const bool glu = l.e_act == LCC_EXPERT_CLAMP_GLU || l.e_act == LCC_EXPERT_SILU_GLU;
             wm = std::max(wm, ld8(l.e_shared_ff));            // the shared expert's hidden row
             // logits row: every router output (real + identity experts), then the shared expert's gate
             moe_e = std::max(moe_e, l.e_experts + l.e_identity); moe_top = std::max(moe_top, l.e_top);
@@ -143,7 +163,7 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
         else if (l.ff > 0) { wp = std::max(wp, ld8(2 * l.ff)); wm = std::max(wm, ld8(l.ff)); }
     }
     L.moe_e = moe_e; L.moe_top = moe_top; L.moe_rows = moe_rows;
-    L.w_proj = wp; L.w_proj2 = wp2; L.w_mid = wm; L.w_y = wy; L.w_q = wq; L.w_f = wf;
+    L.w_proj = wp; L.w_proj2 = wp2; L.w_mid = wm; L.w_y = wy; L.w_q = wq; L.w_f = wf; L.w_vkeep = wvk;
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes); return o; };
     const int W = m->d.width;
@@ -170,6 +190,7 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
     L.o1 = take(nt * ld8(W) * es);
     L.o2 = take(nt * ld8(W) * es);
     L.xf = take(nw * ld8(W) * es);
+    L.vkeep = take(nt * wvk * es);
     L.scan_floats = NT >= lcc::kScanChunkedMin ? scan_floats : 0;   // a decode-only workspace has no use for it
     L.scan = take(L.scan_floats * 4);
     L.split_floats = split_floats;
@@ -192,7 +213,8 @@ int linear(const lcc_seq_model* m, const void* x, int ldx, const void* W, const 
     const int Np = m->d.rows_padded8 ? ld8(N) : N;
     if (act != lcc::ACT_NONE && bias) return -2;
     if (m->use_tc && m->d.dtype == LCC_DT_BF16 && (!y_f32 || (!bias && act == lcc::ACT_NONE)) && (!bias || bias_st) && M >= 16 &&
-        (Np >= 32 || y_f32) && K >= 64 && (K % 8) == 0 && (Np % 8) == 0 && ldy >= Np && (ldx % 8) == 0 && (ldy % 8) == 0) {
+        (Np >= 32 || y_f32) && K >= 64 && (K % 8) == 0 && (Np % 8) == 0 && ldy >= Np && (ldx % 8) == 0 && (ldy % 8) == 0 &&
+        ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 16) == 0) {   // (a slice of a wider row may start anywhere)
         lcc::GemmArgs a;
         a.c_f32 = y_f32;
         a.A = x; a.B = W; a.C = y; a.M = M; a.N = Np; a.K = K; a.lda = ldx; a.ldb = K; a.ldc = ldy;
@@ -239,9 +261,12 @@ lcc_seq_model* lcc_seq_model_create(lcc_ctx* ctx, const lcc_seq_model_desc* desc
     if (desc->width < 1 || desc->vocab < 1 || desc->n_layers < 1) return fail("bad sizes");
     if (desc->dtype != LCC_DT_BF16 && desc->dtype != LCC_DT_F32) return fail("unknown storage type");
     if (!desc->embed || !desc->final_norm_f32 || !desc->head) return fail("missing weights");
-    const bool hc = desc->block == LCC_BLOCK_PRENORM_HC, par = desc->block == LCC_BLOCK_PARALLEL;
+    const bool hc = desc->block == LCC_BLOCK_PRENORM_HC, par = desc->block == LCC_BLOCK_PARALLEL, bn = desc->block == LCC_BLOCK_BRANCHNORM;
     const bool dyt = desc->norm_kind == LCC_NORM_DYT;
-    if (desc->block != LCC_BLOCK_POSTNORM && !hc && !par) return fail("unknown block form");
+    if (desc->block != LCC_BLOCK_POSTNORM && !hc && !par && !bn) return fail("unknown block form");
+    if (bn && (desc->canon_taps < 1 || desc->canon_taps > 8)) return fail("1 to 8 taps in the convolution in front of a mixer");
+    bool vkeep_seen = false;
+    int vkeep_cols = 0;
     if (desc->norm_kind != LCC_NORM_RMS && !dyt) return fail("unknown norm kind");
     if (dyt && (!par || !desc->final_norm_bias_f32)) return fail("the Dynamic-Tanh norm is served in parallel blocks and needs its bias");
     if (hc && (desc->streams < 1 || desc->streams > 8)) return fail("1 to 8 residual streams");
@@ -250,23 +275,26 @@ lcc_seq_model* lcc_seq_model_create(lcc_ctx* ctx, const lcc_seq_model_desc* desc
         if (l.ff_kind == LCC_FF_MOE) {
             if (l.e_experts < 1 || l.e_experts > 512 || l.e_top < 1 || l.e_top > l.e_experts + std::max(l.e_identity, 0) || l.e_ff < 1 || l.e_shared_ff < 0)
                 return fail("routed feed-forward: unsupported sizes");
-            if ((!par && !l.norm2_f32) || !l.e_router || !l.e_correction_f32 || !l.e_up || !l.e_down || (l.e_shared_ff > 0 && (!l.e_shared_up || !l.e_shared_down)))
+            if ((!par && !l.norm2_f32) || !l.e_router || (!l.e_correction_f32 && l.e_router_kind != LCC_ROUTER_TOPK_SOFTMAX) || !l.e_up || !l.e_down || (l.e_shared_ff > 0 && (!l.e_shared_up || !l.e_shared_down)))
                 return fail("routed feed-forward: missing weights");
             const int outs = l.e_experts + l.e_identity;
             if (l.e_identity < 0 || outs > 512 || l.e_top > outs || (l.e_identity > 0 && (l.e_shared_ff > 0 || !par)))
                 return fail("routed feed-forward: identity experts are served in parallel blocks, without a shared expert");
             if (l.e_groups < 0 || (l.e_groups > 0 && (outs % l.e_groups || l.e_keep < 1 || l.e_keep > l.e_groups || l.e_keep * (outs / l.e_groups) < l.e_top)))
                 return fail("routed feed-forward: the kept groups must be equal groups that hold at least `top` experts");
-            if (l.e_router_kind != LCC_ROUTER_SIGMOID && l.e_router_kind != LCC_ROUTER_SOFTMAX) return fail("unknown router kind");
-            if (l.e_act != LCC_EXPERT_RELU2 && l.e_act != LCC_EXPERT_CLAMP_GLU) return fail("unknown expert activation");
-            if (l.e_up_il16 && (l.e_act != LCC_EXPERT_CLAMP_GLU || l.e_ff % 16)) return fail("interleaved gate / up rows need a gated expert width that is a multiple of 16");
+            if (l.e_router_kind != LCC_ROUTER_SIGMOID && l.e_router_kind != LCC_ROUTER_SOFTMAX && l.e_router_kind != LCC_ROUTER_TOPK_SOFTMAX) return fail("unknown router kind");
+            if (l.e_router_kind == LCC_ROUTER_TOPK_SOFTMAX && (l.e_identity > 0 || l.e_groups > 0 || l.e_shared_ff > 0))
+                return fail("routed feed-forward: weights over the chosen logits combine with neither identity experts, groups nor a shared expert");
+            if (l.e_act != LCC_EXPERT_RELU2 && l.e_act != LCC_EXPERT_CLAMP_GLU && l.e_act != LCC_EXPERT_SILU_GLU) return fail("unknown expert activation");
+            if (l.e_up_il16 && (l.e_act == LCC_EXPERT_RELU2 || l.e_ff % 16)) return fail("interleaved gate / up rows need a gated expert width that is a multiple of 16");
         } else if (l.ff_kind != LCC_FF_GLU && l.ff_kind != LCC_FF_MLP) {
             return fail("unknown feed-forward kind");
         }
         if (!l.norm1_f32 || (l.ff > 0 && ((!par && !l.norm2_f32) || !l.ff_in || !l.ff_out))) return fail("missing norm / feed-forward weights");
         if (dyt && !l.norm1_bias_f32) return fail("missing norm bias");
         if (par && l.type != LCC_MIX_ATTENTION) return fail("a parallel block takes the attention mixer");
-        if (!par && l.type == LCC_MIX_ATTENTION) return fail("the attention mixer is served in parallel blocks");
+        if (!par && !bn && l.type == LCC_MIX_ATTENTION) return fail("the attention mixer is served in parallel blocks and in blocks normed on the sublayer's output");
+        if (bn && l.type == LCC_MIX_PARALLEL) return fail("the parallel mixer merges its branches in a post-norm block");
         if (hc && (!l.hc1_f32 || ((l.ff > 0 || l.ff_kind == LCC_FF_MOE) && !l.hc2_f32))) return fail("missing stream weights");
         if (hc && l.type == LCC_MIX_PARALLEL) return fail("the parallel mixer merges its branches in a post-norm block");
         if (l.type == LCC_MIX_SSD) {
@@ -298,15 +326,29 @@ lcc_seq_model* lcc_seq_model_create(lcc_ctx* ctx, const lcc_seq_model_desc* desc
             } else if (!l.a_latent_norm_f32) {
                 return fail("latent attention layer: missing weights");
             }
-            if (!l.a_in || !l.a_uk_t || !l.a_uv || !l.a_sink_f32 || !l.a_out || !l.rot_inv_freq_f32)
+            if (!l.a_in || !l.a_uk_t || !l.a_uv || !l.a_out || !l.rot_inv_freq_f32 || (l.a_q_rank > 0 && (!l.a_uq || !l.a_q_norm_f32)))
                 return fail("latent attention layer: missing weights");
+            if (l.a_q_rank < 0 || l.a_window < 0) return fail("latent attention layer: unsupported sizes");
         } else if (l.type == LCC_MIX_ATTENTION) {
             if (l.m_heads < 1 || l.m_kv_heads < 1 || l.m_heads % l.m_kv_heads || l.m_dim < 1 || l.m_vdim < 1 || l.m_rot_dims < 0 ||
                 (l.m_rot_dims & 1) || l.m_rot_dims > l.m_dim || (l.m_value_keys && l.m_vdim != l.m_dim) || l.m_gate < LCC_GATE_NONE ||
                 l.m_gate > LCC_GATE_CHANNEL)
                 return fail("attention layer: unsupported sizes");
-            if (!l.m_in || !l.m_qnorm_f32 || !l.m_knorm_f32 || !l.m_out || (l.m_rot_dims > 0 && !l.rot_inv_freq_f32))
+            if (!l.m_in || (!l.m_unit_norm && (!l.m_qnorm_f32 || !l.m_knorm_f32)) || !l.m_out || (l.m_rot_dims > 0 && !l.rot_inv_freq_f32))
                 return fail("attention layer: missing weights");
+            if (l.m_vmix_role < 0 || l.m_vmix_role > 2 || (l.m_vmix_role && l.m_value_keys)) return fail("attention layer: values are mixed across layers only when they are projected");
+            if (l.m_vmix_role == 1) {
+                if (vkeep_seen) return fail("attention layer: one layer keeps its values for the later ones");
+                vkeep_seen = true; vkeep_cols = l.m_kv_heads * l.m_vdim;
+            }
+            if (l.m_vmix_role == 2 && (!vkeep_seen || vkeep_cols != l.m_kv_heads * l.m_vdim))
+                return fail("attention layer: mixed values need an earlier layer that keeps values of the same shape");
+        } else if (l.type == LCC_MIX_DELTA) {
+            if (l.d_heads < 1 || l.d_kv_heads < 1 || l.d_heads % l.d_kv_heads || l.d_dim < 1 || l.d_dim > 512 || l.d_vdim < 1 || l.d_conv < 1 ||
+                l.d_conv > 8 || l.d_rank_a < 1 || l.d_rank_g < 1)
+                return fail("delta-rule layer: unsupported sizes");
+            if (!l.d_in || !l.d_conv_w_f32 || !l.d_a_up || !l.d_dt_bias_f32 || !l.d_a_log_f32 || !l.d_g_up || !l.d_norm_f32 || !l.d_out)
+                return fail("delta-rule layer: missing weights");
         } else {
             return fail("unknown mixer type");
         }
@@ -352,14 +394,21 @@ int lcc_seq_bind_workspace(lcc_seq_model* m, void* ws, size_t ws_bytes, int max_
     return 0;
 }
 
+size_t lcc_seq_struct_bytes(int which) {
+    return which == 0 ? sizeof(lcc_seq_layer) : (which == 1 ? sizeof(lcc_seq_model_desc) : (which == 2 ? sizeof(lcc_seq_entry) : 0));
+}
+
 int64_t lcc_seq_layer_state_floats(const lcc_seq_model* m, int layer) {
     if (!m || layer < 0 || layer >= (int)m->layers.size()) return -1;
     const lcc_seq_layer& l = m->layers[layer];
     const Dims z = dims_of(l);
-    if (l.type == LCC_MIX_SSD) return (int64_t)z.conv_ch * (l.s_conv - 1) + (int64_t)l.s_heads * l.s_vdim * l.s_state;
-    if (l.type == LCC_MIX_RETENTION) return (int64_t)l.t_heads * l.t_vdim * l.t_dim;
-    if (l.type == LCC_MIX_LATENT || l.type == LCC_MIX_ATTENTION) return 0;
-    return (int64_t)l.r_heads * l.r_vdim * l.r_dim;
+    // in a block whose mixer sits behind a convolution over time, every layer's slot starts with that convolution's last inputs
+    const int64_t canon = (m->d.block == LCC_BLOCK_BRANCHNORM && l.canon_w_f32) ? (int64_t)m->d.width * (m->d.canon_taps - 1) : 0;
+    if (l.type == LCC_MIX_SSD) return canon + (int64_t)z.conv_ch * (l.s_conv - 1) + (int64_t)l.s_heads * l.s_vdim * l.s_state;
+    if (l.type == LCC_MIX_RETENTION) return canon + (int64_t)l.t_heads * l.t_vdim * l.t_dim;
+    if (l.type == LCC_MIX_LATENT || l.type == LCC_MIX_ATTENTION) return canon;
+    if (l.type == LCC_MIX_DELTA) return canon + (int64_t)z.d_conv_ch * (l.d_conv - 1) + (int64_t)l.d_heads * l.d_vdim * l.d_dim;
+    return canon + (int64_t)l.r_heads * l.r_vdim * l.r_dim;
 }
 
 int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entries, int page_size, const int32_t* want_rows,
@@ -387,8 +436,11 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
     uint8_t* o1 = ws + L.o1; uint8_t* o2 = ws + L.o2; uint8_t* xf = ws + L.xf;
     float* scan_ws = L.scan_floats ? (float*)(ws + L.scan) : nullptr;
     float* split_ws = L.split_floats ? (float*)(ws + L.split) : nullptr;
-    const bool hc = d.block == LCC_BLOCK_PRENORM_HC, par = d.block == LCC_BLOCK_PARALLEL;
+    const bool hc = d.block == LCC_BLOCK_PRENORM_HC, par = d.block == LCC_BLOCK_PARALLEL, bn = d.block == LCC_BLOCK_BRANCHNORM;
     const int NS = hc ? d.streams : 1;
+    uint8_t* vkeep = ws + L.vkeep;
+    // blocks normed on the sublayer's output: does layer i read the residual stream through a convolution over time?
+    auto canon_of = [&](int i) { return bn && i < d.n_layers && m->layers[i].canon_w_f32 != nullptr; };
     // parallel blocks: the norm that opens layer i (none past the last layer)
     auto norm_of = [&](int i) {
         if (i >= d.n_layers) return lcc::NormSpec{d.norm_kind, nullptr, nullptr, 0.f, d.eps};
@@ -420,7 +472,7 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
         for (int e = 0; e < n_entries; ++e) {
             const lcc_seq_entry& en = entries[e];
             STEP(lcc::embed_sinusoid(dt, en.ids, en.scalars ? en.scalars + LCC_SC_SEQ_LEN : nullptr, d.embed, d.vocab, d.embed_scale,
-                                     d.inv_freq_f32, x32 + (size_t)r0 * W * NS, hc ? nullptr : xa + (size_t)r0 * W * es, en.n_new, W,
+                                     d.inv_freq_f32, x32 + (size_t)r0 * W * NS, (hc || canon_of(0)) ? nullptr : xa + (size_t)r0 * W * es, en.n_new, W,
                                      pos_of(en), s, NS), "embedding");
             r0 += en.n_new;
         }
@@ -437,7 +489,58 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
             LCC_FAIL(m->ctx, -100, "stream fork failed");
         cudaStream_t fs = fork_ff ? m->side : s;
         if (hc) STEP(boundary(l.hc1_f32, l.norm1_f32, (layer_dump && li > 0) ? layer_dump + (size_t)(li - 1) * T * W : nullptr), "stream boundary");
-        if (l.type == LCC_MIX_RETENTION) {
+        // what precedes the mixer's own state in the layer's slot
+        const size_t st_off = canon_of(li) ? (size_t)W * (d.canon_taps - 1) : 0;
+        if (canon_of(li)) {
+            // the mixer reads x + conv(x): fp32 rows of the residual stream in, rows in the storage type out; the convolution's last
+            // inputs are the head of the layer's state slot
+            int r0 = 0;
+            for (int e = 0; e < n_entries; ++e) {
+                const lcc_seq_entry& en = entries[e];
+                float* st = en.layer_state[li];
+                if (!st && d.canon_taps > 1) LCC_FAIL(m->ctx, -2, "lcc_seq_forward: entry %d has no state for layer %d", e, li);
+                STEP(lcc::causal_conv(dt, x32 + (size_t)r0 * W, W, xa + (size_t)r0 * W * es, W, l.canon_w_f32, nullptr, st, en.n_new, W,
+                                      d.canon_taps, pos_of(en), s, lcc::ConvOpts{true, false, true}), "input convolution");
+                r0 += en.n_new;
+            }
+        }
+        if (l.type == LCC_MIX_DELTA) {
+            // [q | k | v | beta | decay-down | gate-down] -> causal convolution + silu on q, k, v -> decay-up (fp32) -> log decays
+            // and beta -> delta rule (unit q, k inside) -> gate-up -> unit-rms heads x weight x sigmoid(gate) -> out-proj
+            const int ldp = z.d_proj, ldm = z.d_conv_ch, H = l.d_heads, HN = H * l.d_dim, ldv = ld8(z.d_nv);
+            STEP(linear(m, xa, W, l.d_in, nullptr, proj, ldp, false, T, z.d_proj, W, s), "delta-rule in-proj");
+            STEP(linear(m, proj + (size_t)z.d_a1 * es, ldp, l.d_a_up, nullptr, f1, HN, true, T, HN, l.d_rank_a, s), "decay projection");
+            STEP(lcc::delta_gates(dt, f1, l.d_dt_bias_f32, l.d_a_log_f32, proj + (size_t)z.d_b * es, ldp, f2, T, H, l.d_dim, s), "decays and write strengths");
+            STEP(linear(m, proj + (size_t)z.d_g1 * es, ldp, l.d_g_up, nullptr, proj2, ldv, false, T, z.d_nv, l.d_rank_g, s), "gate projection");
+            int r0 = 0;
+            for (int e = 0; e < n_entries; ++e) {
+                const lcc_seq_entry& en = entries[e];
+                float* st = en.layer_state[li];
+                if (!st) LCC_FAIL(m->ctx, -2, "lcc_seq_forward: entry %d has no state for layer %d", e, li);
+                st += st_off;
+                const lcc::SeqPos pos = pos_of(en);
+                uint8_t* qkv = mid + (size_t)r0 * ldm * es;
+                STEP(lcc::causal_conv(dt, proj + (size_t)r0 * ldp * es, ldp, qkv, ldm, l.d_conv_w_f32, nullptr, st, en.n_new, z.d_conv_ch,
+                                      l.d_conv, pos, s, lcc::ConvOpts{false, true, false}), "causal convolution");
+                lcc::ScanArgs a{};
+                a.dt = dt;
+                a.k = qkv + (size_t)z.d_k * es; a.ld_k = ldm;
+                a.c = qkv; a.ld_c = ldm;
+                a.u = qkv + (size_t)z.d_v * es; a.ld_u = ldm;
+                a.a = f1 + (size_t)r0 * HN; a.vec_decay = 1;
+                a.sc = f2 + (size_t)r0 * H; a.skip = nullptr; a.cs = 1.f / sqrtf((float)l.d_dim);
+                a.state = st + (size_t)z.d_conv_ch * (l.d_conv - 1);
+                a.y = y32 + (size_t)r0 * z.d_nv; a.ld_y = z.d_nv;
+                a.S = en.n_new; a.heads = H; a.heads_per_group = H / l.d_kv_heads; a.N = l.d_dim; a.P = l.d_vdim;
+                a.ws = nullptr; a.ws_floats = 0;
+                a.delta = true; a.unit_eps = 1e-6f;
+                STEP(lcc::gated_scan(a, pos, s), "delta-rule recurrence");
+                r0 += en.n_new;
+            }
+            STEP(lcc::gated_group_norm(dt, y32, z.d_nv, proj2, ldv, l.d_norm_f32, l.d_vdim, mid2, ldv, T, z.d_nv, l.d_vdim, 2, d.eps, s),
+                 "head norm + gate");
+            STEP(linear(m, mid2, ldv, l.d_out, nullptr, o1, W, false, T, W, z.d_nv, s), "delta-rule out-proj");
+        } else if (l.type == LCC_MIX_RETENTION) {
             // [q | k | v | gate] -> rotary q, k (k scaled), everything that enters the recurrence packed as fp32 -> recurrence
             // with one constant decay per head -> unit-rms heads x silu(gate) -> out-proj
             const int ldp = ld8(z.t_proj), ldv = ld8(z.t_nv), H = l.t_heads;
@@ -447,6 +550,7 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
                 const lcc_seq_entry& en = entries[e];
                 float* st = en.layer_state[li];
                 if (!st) LCC_FAIL(m->ctx, -2, "lcc_seq_forward: entry %d has no state for layer %d", e, li);
+                st += st_off;
                 const lcc::SeqPos pos = pos_of(en);
                 float* pk = q32 + (size_t)r0 * z.t_pack;
                 const lcc::RotarySegment seg[3] = {
@@ -479,24 +583,35 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
             const int ldp = ld8(z.a_proj), ldl = ld8(z.a_lat), ldo = ld8(z.a_o), H = l.a_heads, QH = l.a_dim + l.a_rot_dim;
             const int src = l.a_kv_from >= 0 ? l.a_kv_from : li;
             STEP(linear(m, xa, W, l.a_in, nullptr, proj, ldp, false, T, z.a_proj, W, s), "latent attention in-proj");
+            // queries through a latent of their own: RMS norm of the projection's first block, then the up-projection to the heads
+            const uint8_t* qsrc = proj; int ldq = ldp;
+            if (l.a_q_rank > 0) {
+                const int ldc = ld8(l.a_q_rank);
+                STEP(lcc::slice_rmsnorm(dt, proj, ldp, l.a_q_norm_f32, d.eps, mid2, ldc, T, l.a_q_rank, s), "query latent norm");
+                STEP(linear(m, mid2, ldc, l.a_uq, nullptr, proj2, ld8(z.a_nq), false, T, z.a_nq, l.a_q_rank, s), "query up-projection");
+                qsrc = proj2; ldq = ld8(z.a_nq);
+            }
+            const bool own_q = l.a_q_rank > 0;
+            const lcc::AttnOpts lo{l.a_window, l.a_sink_f32 == nullptr, false};
             int r0 = 0;
             for (int e = 0; e < n_entries; ++e) {
                 const lcc_seq_entry& en = entries[e];
                 if (!en.k_pages || !en.k_pages[src] || !en.page_table)
                     LCC_FAIL(m->ctx, -2, "lcc_seq_forward: entry %d has no pages for layer %d", e, src);
-                STEP(lcc::latent_kv_append(dt, proj + (size_t)r0 * ldp * es, ldp, l.a_kv_from < 0, l.a_latent_norm_f32, d.eps,
+                STEP(lcc::latent_kv_append(dt, proj + ((size_t)r0 * ldp + (own_q ? z.a_qin : 0)) * es, ldp, l.a_kv_from < 0, l.a_latent_norm_f32, d.eps,
                                            l.rot_inv_freq_f32, l.rot_mag, q32 + (size_t)r0 * H * z.a_kd, en.k_pages[src], en.page_table,
-                                           page_size, en.n_new, H, l.a_dim, l.a_rot_dim, l.a_rank, pos_of(en), s), "latent cache append");
+                                           page_size, en.n_new, H, l.a_dim, l.a_rot_dim, l.a_rank, pos_of(en), s,
+                                           own_q ? qsrc + (size_t)r0 * ldq * es : nullptr, ldq), "latent cache append");
                 r0 += en.n_new;
             }
-            STEP(linear_heads(m, proj, ldp, QH, l.a_uk_t, q32, H * z.a_kd, z.a_kd, true, H, T, l.a_rank, l.a_dim, s), "query absorption");
+            STEP(linear_heads(m, qsrc, ldq, QH, l.a_uk_t, q32, H * z.a_kd, z.a_kd, true, H, T, l.a_rank, l.a_dim, s), "query absorption");
             r0 = 0;
             for (int e = 0; e < n_entries; ++e) {
                 const lcc_seq_entry& en = entries[e];
-                STEP(lcc::attn_chunk_sink(dt, q32 + (size_t)r0 * H * z.a_kd, en.k_pages[src], en.k_pages[src], en.page_table, page_size,
-                                          proj + ((size_t)r0 * ldp + z.a_gate) * es, ldp, mid + (size_t)r0 * ldl * es, ldl, en.n_new, H, 1,
-                                          z.a_kd, l.a_rank, 0, l.a_scale, m->use_tc, pos_of(en), s, l.a_sink_f32, z.a_kd, split_ws, L.split_floats,
-                                          en.past + en.n_new), "latent attention");
+                STEP(lcc::attn_masked(dt, q32 + (size_t)r0 * H * z.a_kd, en.k_pages[src], en.k_pages[src], en.page_table, page_size,
+                                      l.a_gate ? proj + ((size_t)r0 * ldp + z.a_gate) * es : nullptr, ldp, mid + (size_t)r0 * ldl * es, ldl, en.n_new, H, 1,
+                                      z.a_kd, l.a_rank, 0, l.a_scale, m->use_tc, pos_of(en), s, lo, l.a_sink_f32, z.a_kd, split_ws, L.split_floats,
+                                      en.past + en.n_new), "latent attention");
                 r0 += en.n_new;
             }
             STEP(linear_heads(m, mid, ldl, l.a_rank, l.a_uv, mid2, ldo, l.a_vdim, false, H, T, l.a_vdim, l.a_rank, s), "value up-projection");
@@ -515,9 +630,14 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
                 const lcc::SeqPos pos = pos_of(en);
                 uint8_t* pr = proj + (size_t)r0 * ldp * es;
                 float* q = q32 + (size_t)r0 * z.m_nq;
+                // values mixed across layers: the first such layer keeps its rows as projected, later ones cache a blend with them
+                const int ldk = ld8(z.m_nv);
+                const lcc::AppendOpts apo{l.m_unit_norm != 0, l.m_temp_f32,
+                                          l.m_vmix_role == 2 ? vkeep + (size_t)r0 * ldk * es : nullptr, ldk, l.m_vmix,
+                                          l.m_vmix_role == 1 ? vkeep + (size_t)r0 * ldk * es : nullptr, ldk};
                 STEP(lcc::qk_headnorm_rope_append(dt, pr, ldp, z.m_vcol, l.m_qnorm_f32, l.m_knorm_f32, d.eps, l.rot_inv_freq_f32, l.rot_mag,
                                                   l.m_rot_dims, l.m_rot_pairs, q, en.k_pages[li], en.v_pages[li], en.page_table, page_size,
-                                                  en.n_new, l.m_heads, l.m_kv_heads, l.m_dim, l.m_vdim, pos, s), "q/k norm + rotary + cache append");
+                                                  en.n_new, l.m_heads, l.m_kv_heads, l.m_dim, l.m_vdim, pos, s, &apo), "q/k norm + rotary + cache append");
                 STEP(lcc::attn_masked(dt, q, en.k_pages[li], en.v_pages[li], en.page_table, page_size,
                                       z.m_ngate ? pr + (size_t)z.m_gate * es : nullptr, ldp, mid + (size_t)r0 * ldo * es, ldo, en.n_new,
                                       l.m_heads, l.m_kv_heads, l.m_dim, l.m_vdim, l.m_chunk, l.m_scale, m->use_tc, pos, s, ao, nullptr, 0,
@@ -535,6 +655,7 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
                 const lcc_seq_entry& en = entries[e];
                 float* st = en.layer_state[li];
                 if (!st) LCC_FAIL(m->ctx, -2, "lcc_seq_forward: entry %d has no state for layer %d", e, li);
+                st += st_off;
                 const lcc::SeqPos pos = pos_of(en);
                 uint8_t* pr = proj + (size_t)r0 * ldp * es;
                 uint8_t* xbc = mid + (size_t)r0 * ldm * es;
@@ -615,17 +736,23 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
         // ---- the mixer's output is in o1 ----
         if (hc) pend_hc = l.hc1_f32;
         else if (par) {}   // the feed-forward reads the same normed row; the residual sum closes the layer
+        else if (bn)       // x <- x + norm1(mixer); the feed-forward (or a next layer without a convolution) reads the new row
+            STEP(lcc::branch_norm_residual(dt, x32, o1, W, nullptr, l.norm1_f32, d.eps, (has_ff || (li + 1 < d.n_layers && !canon_of(li + 1))) ? xa : nullptr,
+                                           T, W, s), "norm1 + residual");
         else if (l.type != LCC_MIX_PARALLEL)
             STEP(lcc::postnorm_residual(dt, x32, xa, o1, W, nullptr, nullptr, 0, nullptr, l.norm1_f32, d.alpha, d.eps, T, W, s), "norm1");
         if (has_ff && hc) STEP(boundary(l.hc2_f32, l.norm2_f32, nullptr), "stream boundary");
-        lcc::MoeCombine par_mc{};       // parallel block: the routed feed-forward's row is formed by the layer's residual kernel
+        lcc::MoeCombine par_mc{};       // parallel block and output-normed block: the routed feed-forward's row is formed by the layer's residual kernel
         bool par_is_mc = false;
         if (l.ff_kind == LCC_FF_MOE) {
             // E real experts own row lists; the router has EO = E + identity outputs
-            const bool glu = l.e_act == LCC_EXPERT_CLAMP_GLU;
+            const bool glu = l.e_act == LCC_EXPERT_CLAMP_GLU || l.e_act == LCC_EXPERT_SILU_GLU;
+            // the gated activation g * sigmoid(alpha g) * (u + up_bias) with its clamp: the plain silu form has no clamp
+            const bool silu_glu = l.e_act == LCC_EXPERT_SILU_GLU;
+            const float glu_limit = silu_glu ? INFINITY : l.e_limit, glu_alpha = silu_glu ? 1.f : 1.702f, glu_up_bias = silu_glu ? 0.f : 1.f;
             const int E = l.e_experts, EO = E + l.e_identity, K = l.e_top, lde = ld8(EO + 1), NH = glu ? 2 * l.e_ff : l.e_ff, ldh = ld8(NH),
                       ldg = ld8(l.e_ff), ldw8 = ld8(W), lds = ld8(l.e_shared_ff);
-            const lcc::MoeRouterOpts ro{l.e_router_kind == LCC_ROUTER_SOFTMAX, l.e_identity, l.e_groups, l.e_keep};
+            const lcc::MoeRouterOpts ro{l.e_router_kind == LCC_ROUTER_SOFTMAX, l.e_identity, l.e_groups, l.e_keep, l.e_router_kind == LCC_ROUTER_TOPK_SOFTMAX};
             const int up_act = glu ? lcc::ACT_NONE : lcc::ACT_RELU2;
             float* mf = (float*)(ws + L.moe_f);
             float* logit = mf; float* wsel = mf + (size_t)T * lde; float* sgate = wsel + (size_t)T * K;
@@ -667,10 +794,11 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
                 a.A = ex; a.B = l.e_up; a.C = epi_glu ? eg : eh; a.M = n_tiles * kMoeTile; a.N = NH; a.K = W; a.lda = ldw8; a.ldb = W;
                 a.ldc = epi_glu ? ldg : ldh;
                 a.bias = nullptr; a.residual = nullptr; a.ldr = 0; a.block_n = 0;
-                a.epi = epi_glu ? lcc::EPI_CLAMP_GLU : (glu ? lcc::EPI_NONE : lcc::EPI_RELU2); a.epi_param = l.e_limit;
+                a.epi = epi_glu ? lcc::EPI_CLAMP_GLU : (glu ? lcc::EPI_NONE : lcc::EPI_RELU2);
+                a.epi_param = glu_limit; a.epi_alpha = glu_alpha; a.epi_up_bias = glu_up_bias;
                 a.tile_group = tile_group; a.groups = E;
                 STEP(lcc::gemm_bf16_tn(a, m->ctx->num_sms, fs), "experts up");
-                if (glu && !epi_glu) STEP(lcc::glu_clamp_swish(dt, eh, ldh, eg, ldg, n_tiles * kMoeTile, l.e_ff, l.e_limit, fs), "expert activation");
+                if (glu && !epi_glu) STEP(lcc::glu_clamp_swish(dt, eh, ldh, eg, ldg, n_tiles * kMoeTile, l.e_ff, glu_limit, fs, false, glu_alpha, glu_up_bias), "expert activation");
                 a.A = glu ? eg : eh; a.B = l.e_down; a.C = eo; a.N = W; a.K = l.e_ff; a.lda = glu ? ldg : ldh; a.ldb = l.e_ff; a.ldc = ldw8; a.epi = lcc::EPI_NONE;
                 STEP(lcc::gemm_bf16_tn(a, m->ctx->num_sms, fs), "experts down");
             } else {
@@ -679,7 +807,10 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
                 g.W = l.e_up; g.ldw = W; g.w_stride = (int64_t)NH * W;
                 g.C = glu ? eg : eh; g.ldc = glu ? ldg : ldh; g.c_stride = 0; g.c_f32 = false;
                 g.groups = E; g.M = T; g.N = l.e_ff; g.K = W; g.act = up_act;
-                if (glu) { g.glu_F = l.e_ff; g.glu_il16 = l.e_up_il16 != 0; g.glu_limit = l.e_limit; g.glu_tmp = eh; g.ld_tmp = ldh; }
+                if (glu) {
+                    g.glu_F = l.e_ff; g.glu_il16 = l.e_up_il16 != 0; g.glu_limit = glu_limit; g.glu_tmp = eh; g.ld_tmp = ldh;
+                    g.glu_alpha = glu_alpha; g.glu_up_bias = glu_up_bias;
+                }
                 STEP(lcc::linear_grouped(g, fs), "experts up");
                 g.glu_F = 0; g.glu_tmp = nullptr;
                 g.A = glu ? eg : eh; g.lda = glu ? ldg : ldh; g.a_rows = nullptr;
@@ -692,7 +823,7 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
             if (hc) {   // the weighted sum of the experts' rows is formed by the boundary kernel that folds it into the streams
                 pend_mc = lcc::MoeCombine{eo, ldw8, posn, wsel, K, shared ? o2 : nullptr, W, sgate};
                 pend_is_mc = true;
-            } else if (par) {   // ... or by the residual kernel that closes the layer; identity experts return the normed row
+            } else if (par || bn) {   // ... or by the residual kernel that closes the layer; identity experts return the normed row
                 par_mc = lcc::MoeCombine{eo, ldw8, posn, wsel, K, shared ? (const void*)o2 : (ident ? (const void*)xa : nullptr), W, sgate};
                 par_is_mc = true;
             } else {
@@ -715,6 +846,10 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
             // x <- x + (mixer + feed-forward), then the next layer's norm of the new row
             STEP(lcc::residual_norm(dt, x32, o1, W, (has_ff && !par_is_mc) ? o2 : nullptr, W, par_is_mc ? &par_mc : nullptr, norm_of(li + 1),
                                     xa, T, W, s), "residual sum + next norm");
+        } else if (has_ff && bn) {
+            // x <- x + norm2(feed-forward); a next layer without a convolution in front of its mixer reads the new row
+            STEP(lcc::branch_norm_residual(dt, x32, par_is_mc ? nullptr : o1, W, par_is_mc ? &par_mc : nullptr, l.norm2_f32, d.eps,
+                                           (li + 1 < d.n_layers && !canon_of(li + 1)) ? xa : nullptr, T, W, s), "norm2 + residual");
         } else if (has_ff) {
             if (hc) pend_hc = l.hc2_f32;
             else STEP(lcc::postnorm_residual(dt, x32, xa, o1, W, nullptr, nullptr, 0, nullptr, l.norm2_f32, d.alpha, d.eps, T, W, s), "norm2");

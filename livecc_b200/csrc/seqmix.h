@@ -60,6 +60,9 @@ struct GroupedLinear {
     // store; the tile kernel writes the 2 * glu_F raw columns to glu_tmp (leading dimension ld_tmp, storage dt, the rows of C)
     // and a row kernel follows.
     int glu_F; bool glu_il16; float glu_limit; void* glu_tmp; int ld_tmp;
+    // the general gated activation g * sigmoid(alpha g) * (u + up_bias) with g = min(gate, limit), u = clamp(up, -limit, limit):
+    // the defaults are the clamped form above; alpha 1, up_bias 0 and an infinite limit give silu(gate) * up
+    float glu_alpha = 1.702f, glu_up_bias = 1.f;
 };
 enum { ACT_NONE = 0, ACT_RELU2 = 1, ACT_GELU_TANH = 2 };   // 2: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))
 int linear_grouped(const GroupedLinear& g, cudaStream_t s);
@@ -71,6 +74,11 @@ int linear_grouped(const GroupedLinear& g, cudaStream_t s);
 // taps-1 inputs of this call.
 int causal_conv_silu(int dt, const void* in, int ld_in, void* out, int ld_out, const float* w, const float* b,
                      float* carry, int S, int C, int taps, SeqPos pos, cudaStream_t s);
+// The same convolution with its parts as options: in_f32: `in` is fp32 whatever dt says (a residual stream); silu: the
+// activation; add_input: out = in + conv(in) (a convolution on a skip path). b may be null (no bias). out has storage dt.
+struct ConvOpts { bool in_f32; bool silu; bool add_input; };
+int causal_conv(int dt, const void* in, int ld_in, void* out, int ld_out, const float* w, const float* b, float* carry,
+                int S, int C, int taps, SeqPos pos, cudaStream_t s, const ConvOpts& opt);
 
 // Step sizes and log decays of a scalar-decay state-space layer: dt = softplus(raw + dt_bias[h]),
 // log decay = -exp(a_log[h]) * dt. raw: [S, heads] slice (storage dt, leading dimension ld); dt_out / decay_out: fp32 [S, heads].
@@ -79,6 +87,10 @@ int ssm_step_decay(int dt, const void* raw, int ld, const float* dt_bias, const 
 // Per-channel log decays of gated linear attention: log(sigmoid(z + bias)) / tau; z: [S, n] slice (storage dt).
 int gla_decay(int dt, const void* z, int ld, const float* bias, float tau, float* decay_out, int S, int n,
               cudaStream_t s);
+// Gates of a delta-rule layer with a decay per key channel: z fp32 [S, heads*N] is replaced by the log decay
+// -exp(a_log[h]) * softplus(z + dt_bias[h*N + n]); beta_out fp32 [S, heads] = sigmoid(b), b: [S, heads] slice (storage dt).
+int delta_gates(int dt, float* z, const float* dt_bias, const float* a_log, const void* b, int ld_b, float* beta_out, int S,
+                int heads, int N, cudaStream_t s);
 
 // Gated linear recurrence, one state matrix St[n, p] (n < N key channels, p < P value channels) per head:
 //     St <- diag(a_t) St + k_t (sc_t * u_t)^T ,   y_t = St^T (cs * c_t) + skip[h] * u_t
@@ -101,6 +113,11 @@ struct ScanArgs {
     float* y; int ld_y;
     int S, heads, heads_per_group, N, P;
     float* ws; size_t ws_floats;   // workspace of the sequence-parallel form (null: token by token)
+    // delta: the delta rule instead of the plain write (token by token in every call; sc is then the write strength beta and
+    // there is no skip term):  St <- diag(a_t) St;  w = sc_t (u_t - St^T k_t);  St <- St + k_t w^T;  y_t = St^T (cs c_t)
+    // unit_eps > 0: k_t and c_t are first divided by sqrt(sum(x^2) + unit_eps) per head (unit vectors)
+    bool delta = false;
+    float unit_eps = 0.f;
 };
 constexpr int kScanChunkedMin = 32;     // rows from which the sequence-parallel form runs
 constexpr int kScanMaxBlocks = 64;      // blocks of 64 rows per pass of the sequence-parallel form (bounds its workspace)
@@ -144,6 +161,11 @@ size_t attn_split_ws_floats(int rows, int Hq, int DV);
 // i sees only j with i - j < window (inside its chunk, when there are chunks too). no_sink: ordinary softmax over the visible
 // keys. gate_channel: the gate slice is [S, Hq*DV], one sigmoid gate per output element.
 struct AttnOpts { int window; bool no_sink; bool gate_channel; };
+// Options of qk_headnorm_rope_append (null: none). unit_norm: q and k heads are divided by their rms without a weight (qn_w, kn_w
+// null; the rotation keeps every pair's length, so norming before it equals norming after it). q_head_scale: fp32 [Hq], one factor
+// per query head on q_out (a temperature on the scores). v_mix: [S, ld_mix] slice (storage dt) of G*DV columns: the cached values
+// are (1 - mix) * v + mix * v_mix in fp32. v_keep: [S, ld_keep] (storage dt) receives the values as projected.
+struct AppendOpts { bool unit_norm; const float* q_head_scale; const void* v_mix; int ld_mix; float mix; void* v_keep; int ld_keep; };
 int attn_masked(int dt, const float* q, const void* k_pages, const void* v_pages, const int* page_table, int page_size,
                 const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D, int DV, int chunk, float scale,
                 bool tensor_cores, SeqPos pos, cudaStream_t s, const AttnOpts& opt, const float* sink = nullptr, int ld_v = 0,
@@ -156,7 +178,7 @@ int attn_masked(int dt, const float* q, const void* k_pages, const void* v_pages
 int qk_headnorm_rope_append(int dt, const void* proj, int ld, int v_col, const float* qn_w, const float* kn_w, float eps,
                             const float* inv_freq, float mag, int rot_dims, int rot_pairs, float* q_out, void* k_pages,
                             void* v_pages, const int* page_table, int page_size, int S, int Hq, int G, int D, int DV, SeqPos pos,
-                            cudaStream_t s);
+                            cudaStream_t s, const AppendOpts* opt = nullptr);
 
 // ---- rotary.cu ----------------------------------------------------------------------------------------------------------
 // Rotary positions in the rotate-half layout: inside a head, channel i < dims/2 of the rotated block pairs with channel
@@ -176,9 +198,11 @@ int rotary_pack_f32(int dt, const void* in, int ld_in, float* out, int ld_out, c
 // With has_kv: c = rms(latent) * norm_w (fp32) and the rotated key part go to the K pages [page][1][page_size][R + DR]
 // at positions past .. past+S-1. Always: the rotated part of each head's query goes to q_out fp32 [S, H, R + DR] at
 // channels R .. R+DR-1 (channels 0 .. R-1 are left for the absorbed unrotated part: W_uk_h^T q_h).
+// q (optional): the query heads [S, ld_q] (storage dt) when they are not the first columns of proj (queries that come through
+// a latent of their own); proj then starts with the latent.
 int latent_kv_append(int dt, const void* proj, int ld, int has_kv, const float* norm_w, float eps, const float* inv_freq,
                      float mag, float* q_out, void* k_pages, const int* page_table, int page_size, int S, int H, int D,
-                     int DR, int R, SeqPos pos, cudaStream_t s);
+                     int DR, int R, SeqPos pos, cudaStream_t s, const void* q = nullptr, int ld_q = 0);
 
 // ---- hyper.cu -----------------------------------------------------------------------------------------------------------
 // One boundary between two sublayers of a pre-norm block on n residual streams xs fp32 [S, n, W]:
@@ -202,7 +226,9 @@ int hyper_boundary(int dt, float* xs, int n, const void* y, int ld_y, const floa
 // are -1, counts / row_off cover the E - identity real experts) and the sum of their weights goes to shared_gate[r] (which
 // must then be given; the logits have no shared-gate column); groups > 0: the E outputs form that many equal groups of
 // neighbours, a group scores as its largest choice score and only members of the `keep` best groups can be chosen.
-struct MoeRouterOpts { bool softmax; int identity; int groups; int keep; };
+// topk_softmax: the choice is by logit (+ correction) and the weights are the softmax over the chosen logits only (times scale);
+// it combines with neither identity experts nor groups. correction may be null (zeros).
+struct MoeRouterOpts { bool softmax; int identity; int groups; int keep; bool topk_softmax = false; };
 int moe_route(const float* logits, int ld, const float* correction, int E, int top, float scale, int* sel, float* weight,
               float* shared_gate, int* counts, int* rank, int S, cudaStream_t s, const MoeRouterOpts* opt = nullptr);
 // moe_route and moe_index (dense lists) in one launch of one CTA, for calls of up to kMoeSmallItems (row, choice) pairs; it
@@ -234,7 +260,8 @@ int embed_sinusoid(int dt, const int64_t* ids, const int* seq_len, const void* t
 int postnorm_residual(int dt, float* x32, void* xa, const void* a, int ld_a, const float* wa, const void* b, int ld_b,
                       const float* wb, const float* w, float alpha, float eps, int S, int W, cudaStream_t s);
 // Grouped RMS norm with a multiplicative silu gate: y: fp32 [S, n]; gate: [S, n] slice (storage dt). Groups of `group`
-// consecutive columns; weight w[c % w_len]. gate_first: out = rms(y * silu(g)) * w, else out = rms(y) * w * silu(g).
+// consecutive columns; weight w[c % w_len]. gate_first 1: out = rms(y * silu(g)) * w; 0: out = rms(y) * w * silu(g);
+// 2: out = rms(y) * w * sigmoid(g).
 int gated_group_norm(int dt, const float* y, int ld_y, const void* gate, int ld_gate, const float* w, int w_len,
                      void* out, int ld_out, int S, int n, int group, int gate_first, float eps, cudaStream_t s);
 // out[r, c] = gelu_tanh(gu[r, c]) * gu[r, F + c]
@@ -242,6 +269,8 @@ int glu_gelu_tanh(int dt, const void* gu, int ld, void* out, int ld_out, int S, 
 // out[i, :] = rms(x32[rows[i], :]) * w  (storage dt)
 int gather_rmsnorm(int dt, const float* x32, const int* rows, const float* w, float eps, void* out, int n_rows, int W,
                    cudaStream_t s);
+// out[r, :n] = rms(in[r, :n]) * w for a slice of rows in the storage type (in, out: leading dimensions in elements; w: fp32 [n])
+int slice_rmsnorm(int dt, const void* in, int ld_in, const float* w, float eps, void* out, int ld_out, int S, int n, cudaStream_t s);
 // A row norm: NORM_RMS x / sqrt(mean(x^2) + eps) * w; NORM_DYT tanh(alpha * x) * w + b (no statistics of the row).
 enum { NORM_RMS = 0, NORM_DYT = 1 };
 struct NormSpec { int kind; const float* w; const float* b; float alpha; float eps; };
@@ -253,9 +282,15 @@ int gather_norm(int dt, const float* x32, const int* rows, const NormSpec& n, vo
 // mc->so may be xa itself (identity experts return the block's normed input): every element is read before it is rewritten.
 int residual_norm(int dt, float* x32, const void* a, int ld_a, const void* b, int ld_b, const MoeCombine* mc, const NormSpec& next,
                   void* xa, int S, int W, cudaStream_t s);
-// out[r, c] = g * sigmoid(1.702 g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit); gate = gu[r, c] and
+// out[r, c] = g * sigmoid(alpha g) * (u + up_bias), g = min(gate, limit), u = clamp(up, -limit, limit); gate = gu[r, c] and
 // up = gu[r, F + c], or with il16 (columns interleaved in groups of 16) gate = gu[r, (c / 16) * 32 + c % 16], up 16 further
-int glu_clamp_swish(int dt, const void* gu, int ld, void* out, int ld_out, int S, int F, float limit, cudaStream_t s, bool il16 = false);
+int glu_clamp_swish(int dt, const void* gu, int ld, void* out, int ld_out, int S, int F, float limit, cudaStream_t s, bool il16 = false,
+                    float alpha = 1.702f, float up_bias = 1.f);
+// A block whose norm sits on the sublayer's output: x32 <- x32 + rms(y) * w in fp32, y = the sublayer's row a [S, ld_a] (storage
+// dt) or, with mc, the routed feed-forward's row formed here as in residual_norm. w: fp32 [W]. xa (optional): the new row in
+// storage dt, what the next sublayer reads.
+int branch_norm_residual(int dt, float* x32, const void* a, int ld_a, const MoeCombine* mc, const float* w, float eps, void* xa,
+                         int S, int W, cudaStream_t s);
 // x <- cap * tanh(x / cap) in place (fp32; cap <= 0: unchanged), then x <- x * scale
 int softcap(float* x, int64_t n, float cap, cudaStream_t s, float scale = 1.f);
 

@@ -24,6 +24,7 @@ register("qwen2_vl", "livecc_b200.engine", "LiveCCB200ForConditionalGeneration")
 register("Bimopel", "livecc_b200.seq_engine", "SeqLMForCausalLM")
 register("Kedelorn", "livecc_b200.seq_engine", "SeqLMForCausalLM")
 register("Dibedra", "livecc_b200.seq_engine", "SeqLMForCausalLM")
+register("Lugizen", "livecc_b200.seq_engine", "SeqLMForCausalLM")
 
 
 def architectures() -> list:

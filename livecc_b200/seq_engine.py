@@ -65,7 +65,21 @@ class SeqWeights:
             return x.to(device=device, dtype=torch.float32).contiguous()
 
         def norm_w(name):   # layer norms whose weights are stored around zero are applied as 1 + w (summed in fp32)
+            if cfg.norm_scalar:     # one number for all coordinates: the kernels read a weight per column
+                if get(name).numel() != 1:
+                    raise ValueError(f"{name} is not a single number")
+                return f32(get(name).to(torch.float32).reshape(1).expand(cfg.width))
             return f32(get(name).to(torch.float32) + cfg.norm_offset) if cfg.norm_offset else f32(get(name))
+
+        def segments(names, pad_cols=None):   # blocks of rows stacked with every block's start at a multiple of 8 rows
+            parts = []
+            for n in names:
+                m = get(n).to(torch.float32)
+                m = m.reshape(m.shape[0], -1)
+                parts.append(m)
+                if m.shape[0] % 8:
+                    parts.append(torch.zeros((-m.shape[0]) % 8, m.shape[1], dtype=m.dtype, device=m.device))
+            return torch.cat(parts, 0)
 
         def check(name, want):
             if shape(name) != tuple(want):
@@ -112,7 +126,25 @@ class SeqWeights:
                     check(a + "in", (n,)), check(a + "out", (n,)), check(a + "mix", (n, n))
                     w[q] = f32(torch.cat([get(a + "in").float().reshape(-1), get(a + "out").float().reshape(-1),
                                           get(a + "mix").float().reshape(-1)]))
-            if L.type == "retention":
+            if cfg.canon_taps:
+                check(p + "canon1", (W, cfg.canon_taps))
+                w["canon"] = f32(get(p + "canon1"))
+            if L.type == "channel_delta":
+                dl, m = L.delta, p + "mix."
+                nk, nv = dl.kv_heads * dl.dim, dl.heads * dl.vdim
+                dl.rank_a, dl.rank_g = int(shape(m + "a1")[0]), int(shape(m + "g1")[0])
+                check(m + "q", (nk, W)), check(m + "k", (nk, W)), check(m + "v", (nv, W)), check(m + "b", (dl.heads, W))
+                check(m + "q.conv", (nk, dl.conv)), check(m + "k.conv", (nk, dl.conv)), check(m + "v.conv", (nv, dl.conv))
+                check(m + "a1", (dl.rank_a, W)), check(m + "a2", (dl.heads * dl.dim, dl.rank_a)), check(m + "dt_bias", (dl.heads * dl.dim,))
+                check(m + "A_log", (dl.heads,)), check(m + "g1", (dl.rank_g, W)), check(m + "g2", (nv, dl.rank_g))
+                check(m + "norm", (dl.vdim,)), check(m + "o", (W, nv))
+                # one input projection [q | k | v | beta | decay-down | gate-down], every block starting at a multiple of 8 rows; the
+                # convolution's taps follow the q, k, v blocks (zero taps on the padding channels)
+                w["d_in"] = segments([m + "q", m + "k", m + "v", m + "b", m + "a1", m + "g1"]).to(device=device, dtype=dtype).contiguous()
+                w["d_conv_w"] = f32(segments([m + "q.conv", m + "k.conv", m + "v.conv"]))
+                w["d_a_up"], w["d_g_up"], w["d_out"] = mat(m + "a2"), mat(m + "g2"), mat(m + "o")
+                w["d_dt_bias"], w["d_a_log"], w["d_norm"] = f32(get(m + "dt_bias")), f32(get(m + "A_log")), f32(get(m + "norm"))
+            elif L.type == "retention":
                 rt, m = L.retention, p + "mix."
                 check(m + "q", (rt.heads * rt.dim, W)), check(m + "k", (rt.heads * rt.dim, W))
                 check(m + "v", (rt.heads * rt.vdim, W)), check(m + "g", (rt.heads * rt.vdim, W)), check(m + "o", (W, rt.heads * rt.vdim))
@@ -124,26 +156,48 @@ class SeqWeights:
                     w["rot_freq"], w["rot_mag"] = rotary(rt.rot)
             elif L.type == "latent_attention":
                 a, m = L.latent, p + "mix."
-                check(m + "q", (a.heads * (a.dim + a.rot_dim), W)), check(m + "g", (a.heads, W))
                 check(m + "uk", (a.heads * a.dim, a.kv_rank)), check(m + "uv", (a.heads * a.vdim, a.kv_rank))
-                check(m + "o", (W, a.heads * a.vdim)), check(m + "sink", (a.heads,))
+                check(m + "o", (W, a.heads * a.vdim))
+                if a.q_rank or (m + "dq") in t:      # queries through a latent of their own: [down | norm | up]
+                    a.q_rank = int(shape(m + "dq")[0])
+                    check(m + "dq", (a.q_rank, W)), check(m + "dq.norm", (a.q_rank,)), check(m + "uq", (a.heads * (a.dim + a.rot_dim), a.q_rank))
+                    rows = [m + "dq"]
+                    w["a_q_norm"], w["a_uq"] = f32(get(m + "dq.norm")), mat(m + "uq")
+                else:
+                    check(m + "q", (a.heads * (a.dim + a.rot_dim), W))
+                    rows = [m + "q"]
                 if a.kv_from < 0:
                     check(m + "dkv", (a.kv_rank + a.rot_dim, W)), check(m + "dkv.norm", (a.kv_rank,))
-                    w["a_in"] = mat(m + "q", m + "dkv", m + "g")
+                    rows.append(m + "dkv")
                     w["a_latent_norm"] = f32(get(m + "dkv.norm"))
-                else:
-                    w["a_in"] = mat(m + "q", m + "g")
+                if a.gate:
+                    check(m + "g", (a.heads, W))
+                    rows.append(m + "g")
+                w["a_in"] = mat(*rows)
                 # query absorption reads each head's key up-projection transposed: [heads][rank][dim]
                 w["a_uk_t"] = get(m + "uk").to(torch.float32).reshape(a.heads, a.dim, a.kv_rank).transpose(1, 2) \
                     .contiguous().to(device=device, dtype=dtype)
                 w["a_uv"] = mat(m + "uv")
-                w["a_sink"] = f32(get(m + "sink"))
+                if a.sink:
+                    check(m + "sink", (a.heads,))
+                    w["a_sink"] = f32(get(m + "sink"))
                 w["a_out"] = mat(m + "o")
                 w["rot_freq"], w["rot_mag"] = rotary(a.rot)
             elif L.type == "attention":
                 a, m = L.attn, p + "mix."
                 check(m + "q", (a.heads * a.dim, W)), check(m + "k", (a.kv_heads * a.dim, W)), check(m + "o", (W, a.heads * a.vdim))
-                check(m + "q.norm", (a.dim,)), check(m + "k.norm", (a.dim,))
+                if not a.unit_norm:
+                    check(m + "q.norm", (a.dim,)), check(m + "k.norm", (a.dim,))
+                    w["m_qnorm"], w["m_knorm"] = f32(get(m + "q.norm")), f32(get(m + "k.norm"))
+                if a.temp:
+                    check(m + "temp", (a.heads,))
+                    w["m_temp"] = f32(get(m + "temp"))
+                if a.v_mix:      # the first such layer keeps its values for the later ones, whose `vmix` blends them in
+                    first = next(j for j, x in enumerate(cfg.layers) if x.type == "attention" and x.attn.v_mix)
+                    if get(m + "vmix").numel() != 1:
+                        raise ValueError(f"{m}vmix is not a single number")
+                    w["m_vmix_role"] = 1 if first == i else 2
+                    w["m_vmix"] = float(get(m + "vmix").to(torch.float32).reshape(-1)[0])
                 rows = [m + "q", m + "k"]
                 if not a.value_keys:
                     check(m + "v", (a.kv_heads * a.vdim, W))
@@ -152,7 +206,6 @@ class SeqWeights:
                     check(m + "g", (a.gate_rows, W))
                     rows.append(m + "g")
                 w["m_in"] = mat(*rows)
-                w["m_qnorm"], w["m_knorm"] = f32(get(m + "q.norm")), f32(get(m + "k.norm"))
                 w["m_out"] = mat(m + "o")
                 if a.rot.dims:
                     w["rot_freq"], w["rot_mag"] = rotary(a.rot)
@@ -205,8 +258,10 @@ class SeqWeights:
                     w["norm2"] = norm_w(p + "norm2")
                 for j in range(e.experts):
                     check(f"{m}e{j}.up", (e.ff, W)), check(f"{m}e{j}.down", (W, e.ff))
-                check(m + "router", (e.outputs, W)), check(m + "correction", (e.outputs,))
-                if e.act == "clamp_glu":
+                check(m + "router", (e.outputs, W))
+                if e.router != "topk_softmax":
+                    check(m + "correction", (e.outputs,))
+                if e.act in ("clamp_glu", "silu_glu"):
                     # each expert's gate and up rows in one matrix, so that one product per expert list yields both. Widths that
                     # are multiples of 16 interleave them in groups of 16 rows (the layout whose activation the tensor-core
                     # product's epilogue forms from neighbouring accumulator columns); other widths keep [gate | up].
@@ -224,7 +279,8 @@ class SeqWeights:
                 else:
                     w["e_up"] = torch.stack([get(f"{m}e{j}.up") for j in range(e.experts)]).to(device=device, dtype=dtype).contiguous()
                 w["e_down"] = torch.stack([get(f"{m}e{j}.down") for j in range(e.experts)]).to(device=device, dtype=dtype).contiguous()
-                w["e_correction"] = f32(get(m + "correction"))
+                if e.router != "topk_softmax":
+                    w["e_correction"] = f32(get(m + "correction"))
                 if e.shared_ff:
                     check(m + "shared.up", (e.shared_ff, W)), check(m + "shared.down", (W, e.shared_ff)), check(m + "shared.sg", (1, W))
                     w["e_router"] = mat(m + "router", m + "shared.sg")     # the shared gate's logit is one more router row
@@ -268,7 +324,7 @@ class SeqLMForCausalLM:
         # sliding-window attention: (kv heads, key size, value size, no chunks, window)
         attn.update({i: (L.attn.kv_heads, L.attn.dim, L.attn.vdim, 0, L.attn.window) for i, L in enumerate(config.layers) if L.type == "attention"})
         # a latent cache is one K pool of [latent | rotary key part] rows; a layer that reads another layer's cache has none
-        attn.update({i: (1, L.latent.kv_rank + L.latent.rot_dim, 0, 0) for i, L in enumerate(config.layers)
+        attn.update({i: (1, L.latent.kv_rank + L.latent.rot_dim, 0, 0, L.latent.window) for i, L in enumerate(config.layers)
                      if L.type == "latent_attention" and L.latent.kv_from < 0})
         self._kv_source = {i: (L.latent.kv_from if L.latent.kv_from >= 0 else i) for i, L in enumerate(config.layers)
                            if L.type == "latent_attention"}
@@ -310,7 +366,14 @@ class SeqLMForCausalLM:
             e.hc1_f32, e.hc2_f32 = p(lw.get("hc1")), p(lw.get("hc2"))
             e.a_kv_from = -1
             e.rot_inv_freq_f32, e.rot_mag = p(lw.get("rot_freq")), lw.get("rot_mag", 1.0)
-            if L.type == "retention":
+            e.canon_w_f32 = p(lw.get("canon"))
+            if L.type == "channel_delta":
+                t = L.delta
+                e.type = _cabi.MIX_DELTA
+                e.d_heads, e.d_kv_heads, e.d_dim, e.d_vdim, e.d_conv, e.d_rank_a, e.d_rank_g = t.heads, t.kv_heads, t.dim, t.vdim, t.conv, t.rank_a, t.rank_g
+                e.d_in, e.d_conv_w_f32, e.d_a_up, e.d_g_up, e.d_out = p(lw["d_in"]), p(lw["d_conv_w"]), p(lw["d_a_up"]), p(lw["d_g_up"]), p(lw["d_out"])
+                e.d_dt_bias_f32, e.d_a_log_f32, e.d_norm_f32 = p(lw["d_dt_bias"]), p(lw["d_a_log"]), p(lw["d_norm"])
+            elif L.type == "retention":
                 t = L.retention
                 e.type = _cabi.MIX_RETENTION
                 e.t_heads, e.t_dim, e.t_vdim, e.t_rot_dims = t.heads, t.dim, t.vdim, t.rot.dims
@@ -320,8 +383,10 @@ class SeqLMForCausalLM:
                 e.type = _cabi.MIX_LATENT
                 e.a_heads, e.a_dim, e.a_rot_dim, e.a_vdim, e.a_rank, e.a_kv_from = a.heads, a.dim, a.rot_dim, a.vdim, a.kv_rank, a.kv_from
                 e.a_scale = a.scale
+                e.a_q_rank, e.a_window, e.a_gate = a.q_rank, a.window, int(a.gate)
+                e.a_uq, e.a_q_norm_f32 = p(lw.get("a_uq")), p(lw.get("a_q_norm"))
                 e.a_in, e.a_latent_norm_f32, e.a_uk_t, e.a_uv = p(lw["a_in"]), p(lw.get("a_latent_norm")), p(lw["a_uk_t"]), p(lw["a_uv"])
-                e.a_sink_f32, e.a_out = p(lw["a_sink"]), p(lw["a_out"])
+                e.a_sink_f32, e.a_out = p(lw.get("a_sink")), p(lw["a_out"])
             elif L.type == "attention":
                 a = L.attn
                 e.type = _cabi.MIX_ATTENTION
@@ -329,7 +394,8 @@ class SeqLMForCausalLM:
                 e.m_rot_dims, e.m_rot_pairs, e.m_sink, e.m_value_keys = a.rot.dims, int(a.rot_pairs), int(a.sink), int(a.value_keys)
                 e.m_gate = {"none": _cabi.GATE_NONE, "head": _cabi.GATE_HEAD, "channel": _cabi.GATE_CHANNEL}[a.gate]
                 e.m_scale = a.scale
-                e.m_in, e.m_qnorm_f32, e.m_knorm_f32, e.m_out = p(lw["m_in"]), p(lw["m_qnorm"]), p(lw["m_knorm"]), p(lw["m_out"])
+                e.m_unit_norm, e.m_vmix_role, e.m_vmix, e.m_temp_f32 = int(a.unit_norm), lw.get("m_vmix_role", 0), lw.get("m_vmix", 0.0), p(lw.get("m_temp"))
+                e.m_in, e.m_qnorm_f32, e.m_knorm_f32, e.m_out = p(lw["m_in"]), p(lw.get("m_qnorm")), p(lw.get("m_knorm")), p(lw["m_out"])
             elif L.type == "mamba2":
                 s = L.ssd
                 e.type = _cabi.MIX_SSD
@@ -351,11 +417,11 @@ class SeqLMForCausalLM:
                 x = L.moe
                 e.ff_kind = _cabi.FF_MOE
                 e.e_experts, e.e_top, e.e_ff, e.e_shared_ff, e.e_scale = x.experts, x.top, x.ff, x.shared_ff, x.scale
-                e.e_router_kind = _cabi.ROUTER_SOFTMAX if x.router == "softmax" else _cabi.ROUTER_SIGMOID
+                e.e_router_kind = {"softmax": _cabi.ROUTER_SOFTMAX, "topk_softmax": _cabi.ROUTER_TOPK_SOFTMAX}.get(x.router, _cabi.ROUTER_SIGMOID)
                 e.e_identity, e.e_groups, e.e_keep, e.e_limit = x.identity, x.groups, x.keep, x.limit
-                e.e_act = _cabi.EXPERT_CLAMP_GLU if x.act == "clamp_glu" else _cabi.EXPERT_RELU2
+                e.e_act = {"clamp_glu": _cabi.EXPERT_CLAMP_GLU, "silu_glu": _cabi.EXPERT_SILU_GLU}.get(x.act, _cabi.EXPERT_RELU2)
                 e.e_up_il16 = lw.get("e_up_il16", 0)
-                e.norm2_f32, e.e_router, e.e_correction_f32 = p(lw.get("norm2")), p(lw["e_router"]), p(lw["e_correction"])
+                e.norm2_f32, e.e_router, e.e_correction_f32 = p(lw.get("norm2")), p(lw["e_router"]), p(lw.get("e_correction"))
                 e.e_up, e.e_down = p(lw["e_up"]), p(lw["e_down"])
                 e.e_shared_up, e.e_shared_down = p(lw.get("e_shared_up")), p(lw.get("e_shared_down"))
             elif L.ff:
@@ -365,7 +431,8 @@ class SeqLMForCausalLM:
             width=cfg.width, vocab=cfg.vocab, n_layers=len(cfg.layers),
             dtype=_cabi.DT_F32 if self.dtype == torch.float32 else _cabi.DT_BF16, rows_padded8=1, eps=cfg.eps, alpha=cfg.alpha,
             embed_scale=cfg.embed_scale, logit_softcap=cfg.logit_softcap,
-            block={"prenorm_hc": _cabi.BLOCK_PRENORM_HC, "parallel": _cabi.BLOCK_PARALLEL}.get(cfg.block, _cabi.BLOCK_POSTNORM), streams=cfg.streams,
+            block={"prenorm_hc": _cabi.BLOCK_PRENORM_HC, "parallel": _cabi.BLOCK_PARALLEL, "branchnorm": _cabi.BLOCK_BRANCHNORM}.get(cfg.block, _cabi.BLOCK_POSTNORM),
+            streams=cfg.streams, canon_taps=cfg.canon_taps,
             norm_kind=_cabi.NORM_DYT if cfg.norm == "dyt" else _cabi.NORM_RMS, final_norm_alpha=w.final_norm_alpha,
             logit_scale=cfg.logit_scale, final_norm_bias_f32=p(w.final_norm_bias),
             embed=p(w.embed), inv_freq_f32=p(w.inv_freq),
