@@ -264,7 +264,7 @@ lcc_seq_model* lcc_seq_model_create(lcc_ctx* ctx, const lcc_seq_model_desc* desc
     const bool hc = desc->block == LCC_BLOCK_PRENORM_HC, par = desc->block == LCC_BLOCK_PARALLEL, bn = desc->block == LCC_BLOCK_BRANCHNORM;
     const bool dyt = desc->norm_kind == LCC_NORM_DYT;
     if (desc->block != LCC_BLOCK_POSTNORM && !hc && !par && !bn) return fail("unknown block form");
-    if (bn && (desc->canon_taps < 1 || desc->canon_taps > 8)) return fail("1 to 8 taps in the convolution in front of a mixer");
+    if (bn && (desc->canon_taps < 0 || desc->canon_taps > 8)) return fail("at most 8 taps in the convolution in front of a mixer");
     bool vkeep_seen = false;
     int vkeep_cols = 0;
     if (desc->norm_kind != LCC_NORM_RMS && !dyt) return fail("unknown norm kind");
@@ -290,6 +290,7 @@ lcc_seq_model* lcc_seq_model_create(lcc_ctx* ctx, const lcc_seq_model_desc* desc
         } else if (l.ff_kind != LCC_FF_GLU && l.ff_kind != LCC_FF_MLP) {
             return fail("unknown feed-forward kind");
         }
+        if (bn && l.canon_w_f32 && desc->canon_taps < 1) return fail("a convolution in front of the mixer needs its tap count");
         if (!l.norm1_f32 || (l.ff > 0 && ((!par && !l.norm2_f32) || !l.ff_in || !l.ff_out))) return fail("missing norm / feed-forward weights");
         if (dyt && !l.norm1_bias_f32) return fail("missing norm bias");
         if (par && l.type != LCC_MIX_ATTENTION) return fail("a parallel block takes the attention mixer");

@@ -115,7 +115,7 @@ def attention_values(h, cfg, t, p):
     return (h @ t[p + "v"].T).view(h.shape[0], int(cfg["kv_heads"]), int(cfg["vdim"]))
 
 
-def attention_mixer(h, cfg, t, p, eps, v_first=None, start=0):
+def attention_mixer(h, cfg, t, p, eps, v_first=None, start=0, use_temp=True):
     """Returns (output, this layer's values as projected). v_first: the values of the first value-mixing layer (None in
     that layer itself and in layers that do not mix)."""
     H, G, D = int(cfg["heads"]), int(cfg["kv_heads"]), int(cfg["dim"])
@@ -127,7 +127,8 @@ def attention_mixer(h, cfg, t, p, eps, v_first=None, start=0):
     rot = cfg.get("rot") or {"dims": 0, "base": 1.0}
     q = rms(rotate_half(q, int(rot["dims"]), float(rot["base"]), start), eps)
     k = rms(rotate_half(k, int(rot["dims"]), float(rot["base"]), start), eps)
-    q = q * t[p + "temp"].view(1, H, 1)
+    if use_temp:
+        q = q * t[p + "temp"].view(1, H, 1)
     if v_first is not None:
         lam = t[p + "vmix"]
         v = (1.0 - lam) * v + lam * v_first
@@ -135,7 +136,7 @@ def attention_mixer(h, cfg, t, p, eps, v_first=None, start=0):
     return o @ t[p + "o"].T, own
 
 
-def latent_attention_mixer(h, cfg, t, p, eps, start=0):
+def latent_attention_mixer(h, cfg, t, p, eps, start=0, window_off=False):
     H, D, DR, DV, R = int(cfg["heads"]), int(cfg["dim"]), int(cfg["rot_dim"]), int(cfg["vdim"]), int(cfg["kv_rank"])
     T = h.shape[0]
     base = float(cfg["rot"]["base"])
@@ -148,7 +149,7 @@ def latent_attention_mixer(h, cfg, t, p, eps, start=0):
     k = torch.cat([(c @ t[p + "uk"].T).view(T, H, D), k_rot.expand(T, H, DR)], -1)
     v = (c @ t[p + "uv"].T).view(T, H, DV)
     qq = torch.cat([q[..., :D], q_rot], -1)
-    o = softmax_attention(qq, k, v, float(cfg["scale"]), int(cfg["mask"]["size"])).reshape(T, -1)
+    o = softmax_attention(qq, k, v, float(cfg["scale"]), 0 if window_off else int(cfg["mask"]["size"])).reshape(T, -1)
     return o @ t[p + "o"].T
 
 
@@ -160,15 +161,19 @@ def expert(h, t, p):
     return (silu(h @ t[p + "gate"].T) * (h @ t[p + "up"].T)) @ t[p + "down"].T
 
 
-def route(h, mlp, t, p):
-    """([T, top] chosen experts, [T, top] weights = softmax over the chosen logits only)."""
+def route(h, mlp, t, p, equal_weights=False):
+    """([T, top] chosen experts, [T, top] weights = softmax over the chosen logits only; equal_weights: 1 / top each instead,
+    which is what the design does not do. A softmax over every logit would differ from the design's by one factor per row,
+    which the norm behind the feed-forward removes again)."""
     z = h @ t[p + "router"].T
     top = torch.topk(z, int(mlp["router"]["top"]), -1)
+    if equal_weights:
+        return top.indices, torch.full_like(top.values, 1.0 / top.values.shape[-1])
     return top.indices, torch.softmax(top.values, -1)
 
 
-def routed_ff(h, mlp, t, p):
-    idx, w = route(h, mlp, t, p)
+def routed_ff(h, mlp, t, p, equal_weights=False):
+    idx, w = route(h, mlp, t, p, equal_weights)
     out = torch.zeros(h.shape[0], t[p + "e0.down"].shape[0], dtype=F64)
     for r in range(h.shape[0]):
         for j, e in enumerate(idx[r].tolist()):
@@ -176,32 +181,42 @@ def routed_ff(h, mlp, t, p):
     return out
 
 
-def forward(cfg, tensors, ids, layer_outputs=False):
-    """Logits [T, vocab] of one sequence (and, with layer_outputs, the residual stream after every layer)."""
+def forward(cfg, tensors, ids, layer_outputs=False, leave_out=()):
+    """Logits [T, vocab] of one sequence (and, with layer_outputs, the residual stream after every layer). leave_out names
+    mechanisms to drop ("canon", "vmix", "temp", "window", "router_weights"): tests use it to show that their weights would
+    expose a product that dropped one."""
     t = {k: v.to(F64) for k, v in tensors.items()}
     eps = float(cfg["norm"]["eps"])
     x = t["embed"][torch.as_tensor(ids, dtype=torch.long)]
     v_first, outs = None, []
     for i, L in enumerate(cfg["layers"]):
         p = f"l{i}."
-        h = x + time_conv(x, t[p + "canon1"]) if p + "canon1" in t else x
+        h = x + time_conv(x, t[p + "canon1"]) if (p + "canon1" in t and "canon" not in leave_out) else x
         mx = L["mixer"]
         if L["type"] == "channel_delta":
             y = channel_delta_mixer(h, mx, t, p + "mix.", eps)
         elif L["type"] == "attention":
-            mixes = bool(mx.get("v_mix"))
-            y, own = attention_mixer(h, mx, t, p + "mix.", eps, v_first if mixes else None)
+            mixes = bool(mx.get("v_mix")) and "vmix" not in leave_out
+            y, own = attention_mixer(h, mx, t, p + "mix.", eps, v_first if mixes else None, use_temp="temp" not in leave_out)
             if mixes and v_first is None:
                 v_first = own
         elif L["type"] == "latent_attention":
-            y = latent_attention_mixer(h, mx, t, p + "mix.", eps)
+            y = latent_attention_mixer(h, mx, t, p + "mix.", eps, window_off="window" in leave_out)
         else:
             raise NotImplementedError(L["type"])
         x = x + scalar_norm(y, t[p + "norm1"], eps)
         mlp = L.get("mlp")
         if mlp is not None:
-            y = dense_ff(x, t, p + "mlp.") if mlp["kind"] == "dense" else routed_ff(x, mlp, t, p + "mlp.")
+            y = dense_ff(x, t, p + "mlp.") if mlp["kind"] == "dense" else routed_ff(x, mlp, t, p + "mlp.", "router_weights" in leave_out)
             x = x + scalar_norm(y, t[p + "norm2"], eps)
         outs.append(x)
     logits = scalar_norm(x, t["final.norm"], eps) @ t["head"].T
     return (logits, torch.stack(outs)) if layer_outputs else logits
+
+
+def greedy(cfg, tensors, prompt, n_new):
+    """The n_new tokens that greedy decoding appends to the prompt (the whole sequence is recomputed for every token)."""
+    ids = list(prompt)
+    for _ in range(n_new):
+        ids.append(int(forward(cfg, tensors, ids)[-1].argmax()))
+    return ids[len(prompt):]
