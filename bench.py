@@ -46,14 +46,15 @@ def parse_args():
                          "path (HF bf16 + flash_attention_2, optionally --liger) on the same B200 = the kernel to beat")
     ap.add_argument("--liger", action="store_true", help="hf_gpu: apply_liger_kernel_to_qwen2_vl() first (REF/demo/infer.py:2-3)")
     ap.add_argument("--model", default="7b", choices=["7b", "small"])
-    ap.add_argument("--arch", default="livecc", choices=["livecc", "seq", "kedelorn", "dibedra"],
+    ap.add_argument("--arch", default="livecc", choices=["livecc", "seq", "kedelorn", "dibedra", "lugizen"],
                     help="livecc: the streaming video workload (default, the headline metric); seq: prefill / decode throughput of "
                          "the hybrid sequence model (Bimopel) beside the Qwen2-style decoder at equal layer sizes; kedelorn: the "
                          "same for Kedelorn (latent attention, retention, routed experts) beside Bimopel and the Qwen2-style decoder; dibedra: "
                          "the same for Dibedra (sliding-window attention, parallel blocks, routed experts) beside Kedelorn and the "
-                         "Qwen2-style decoder")
-    ap.add_argument("--seq-sizes", default="", help="--arch seq / kedelorn / dibedra: comma-separated size names (livecc_b200/seq_bench.py SIZES)")
-    ap.add_argument("--seq-prompt", default="1024,4096", help="--arch seq / kedelorn / dibedra: prompt lengths")
+                         "Qwen2-style decoder; lugizen: the same for Lugizen (delta rule, attention, windowed latent attention, routed "
+                         "experts, sublayers normed on their output) beside Kedelorn and the Qwen2-style decoder")
+    ap.add_argument("--seq-sizes", default="", help="--arch seq / kedelorn / dibedra / lugizen: comma-separated size names (livecc_b200/seq_bench.py SIZES)")
+    ap.add_argument("--seq-prompt", default="1024,4096", help="--arch seq / kedelorn / dibedra / lugizen: prompt lengths")
     ap.add_argument("--seconds", type=int, default=60, help="clip length in seconds of video (2 fps)")
     ap.add_argument("--size", type=int, default=448)
     ap.add_argument("--max-new-tokens", type=int, default=16)
@@ -496,10 +497,10 @@ def run_hf_gpu(args, cfg, config, dev):
 # ------------------------------------------------------------------------------------------------
 def main():
     args = parse_args()
-    if args.arch in ("seq", "kedelorn", "dibedra"):
+    if args.arch in ("seq", "kedelorn", "dibedra", "lugizen"):
         from livecc_b200 import seq_bench
 
-        print(json.dumps(seq_bench.main(args, design={"kedelorn": "Kedelorn", "dibedra": "Dibedra"}.get(args.arch, "Bimopel"))), flush=True)
+        print(json.dumps(seq_bench.main(args, design={"kedelorn": "Kedelorn", "dibedra": "Dibedra", "lugizen": "Lugizen"}.get(args.arch, "Bimopel"))), flush=True)
         return
     from livecc_b200 import runner  # the repo's own multi-GPU plumbing (rank env, NCCL init, barrier + device sync)
 

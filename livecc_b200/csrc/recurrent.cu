@@ -1,12 +1,15 @@
 // Recurrent sequence mixers with state carried from call to call (prefill portions and decode steps run the same
 // kernels): the short causal convolution of a state-space layer, its step sizes and decays, the per-channel decays of
-// gated linear attention, and the gated linear recurrence both share:
+// gated linear attention, the gated linear recurrence both share:
 //     St <- diag(a_t) St + k_t (sc_t u_t)^T ,  y_t = St^T c_t + skip * u_t          (St: N x P per head, fp32)
+// and the gated delta rule (a decay per key channel, then the write beta (v - St^T k) under the key k).
 // Everything that enters the recurrence is fp32; the projections it reads are in the model's storage type.
 #include <math.h>
+#include <stdlib.h>
 
 #include "../../include/livecc_b200.h"
 #include "common.cuh"
+#include "mma.cuh"
 #include "launch.h"
 #include "seqmix.h"
 
@@ -205,116 +208,183 @@ __global__ void __launch_bounds__(kScanThreads) gated_scan_kernel(ScanArgs a, Se
 }
 
 // ---- delta rule ---------------------------------------------------------------------------------------------------------
-// z -> log decay, b -> beta (see delta_gates)
+// Everything the recurrence reads, prepared for all rows at once (one warp per (row, key head)) and laid out head by head, so
+// that the operands of consecutive tokens of one head are contiguous: unit-length k and q (q also times q_scale) and their
+// product k . q, the values as fp32, the decays exp(-exp(a_log[h]) * softplus(z + dt_bias)), and beta = sigmoid(b).
 template <typename T>
-__global__ void delta_gates_kernel(float* __restrict__ z, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
-                                   const T* __restrict__ b, int ld_b, float* __restrict__ beta_out, int S, int heads, int N) {
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const int HN = heads * N;
-    if (i < (int64_t)S * HN) {
-        const int c = (int)(i % HN);
-        z[i] = -expf(a_log[c / N]) * softplus_f(z[i] + dt_bias[c]);
+__global__ void __launch_bounds__(128) delta_pack_kernel(DeltaPackArgs a) {
+    const int wid = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (wid >= a.S * a.G) return;
+    const int t = wid / a.G, g = wid % a.G, N = a.N, P = a.P, hpg = a.H / a.G;
+    const size_t S = a.S;
+    const DeltaOperands o = delta_operands(a.out, a.S, a.H, a.G, N, P);
+    const T* row = (const T*)a.qkv + (size_t)t * a.ld;
+    const T* qr = row + (size_t)g * N;
+    const T* kr = row + a.col_k + (size_t)g * N;
+    float sq = 0.f, sk = 0.f;
+    for (int n = lane; n < N; n += 32) {
+        const float q = ldf(qr + n), k = ldf(kr + n);
+        sq = fmaf(q, q, sq); sk = fmaf(k, k, sk);
     }
-    if (i < (int64_t)S * heads) {
-        const int t = (int)(i / heads), h = (int)(i % heads);
-        beta_out[i] = 1.f / (1.f + expf(-ldf(b + (size_t)t * ld_b + h)));
+    sq = warp_sum(sq); sk = warp_sum(sk);
+    const float rq = (a.unit_eps > 0.f ? 1.f / sqrtf(sq + a.unit_eps) : 1.f) * a.q_scale;
+    const float rk = a.unit_eps > 0.f ? 1.f / sqrtf(sk + a.unit_eps) : 1.f;
+    float* ko = o.k + ((size_t)g * S + t) * N;
+    float* qo = o.q + ((size_t)g * S + t) * N;
+    float kq = 0.f;
+    for (int n = lane; n < N; n += 32) {
+        const float q = ldf(qr + n) * rq, k = ldf(kr + n) * rk;
+        ko[n] = k;
+        qo[n] = q;
+        kq = fmaf(k, q, kq);
+    }
+    kq = warp_sum(kq);
+    if (lane == 0) o.kq[(size_t)g * S + t] = kq;
+    for (int h = g * hpg; h < (g + 1) * hpg; ++h) {
+        const float rate = -expf(a.a_log[h]);
+        const float* z = a.z + ((size_t)t * a.H + h) * N;
+        float* d = a.dec + ((size_t)h * S + t) * N;
+        for (int n = lane; n < N; n += 32) d[n] = expf(rate * softplus_f(z[n] + a.dt_bias[(size_t)h * N + n]));
+        float* vo = o.v + ((size_t)h * S + t) * P;
+        for (int p = lane; p < P; p += 32) vo[p] = ldf(row + a.col_v + (size_t)h * P + p);
+        if (lane == 0) o.beta[(size_t)h * S + t] = 1.f / (1.f + expf(-ldf((const T*)a.b + (size_t)t * a.ld_b + h)));
     }
 }
 
-// The thread layout of gated_scan_kernel (NT state entries of one value channel per thread, JP lanes per channel). Per token:
-// the state decays, the JP lanes reduce St^T k and St^T c together, the write w = beta (u - St^T k) lands, and the read-out is
-// St^T c + (k . c) w: the same value as reading the state after the write, with one reduction round instead of two. With
-// unit_eps the staged k and c rows are brought to unit length first (one warp per token), which also yields k . c.
-template <typename T>
-__global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(ScanArgs a, SeqPos pos) {
-    if (seq_done(pos)) return;
-    extern __shared__ float sm[];
-    const int N = a.N, P = a.P, S = a.S;
-    const int JP = blockDim.x, cols = blockDim.y;
-    const int h = blockIdx.x;
-    const int col = threadIdx.y;
-    const int p = blockIdx.y * cols + col;
-    const int j = threadIdx.x;
-    const int tid = threadIdx.y * JP + threadIdx.x, nthr = cols * JP;
-    const int n0 = j * NT;
-    const int g = h / a.heads_per_group;
-    // shared: k[TT][N], c[TT][N], dec[TT][N], beta[TT], kc[TT], u[TT][cols]
-    float* sk = sm;
-    float* scv = sk + TT * N;
-    float* sd = scv + TT * N;
-    float* sb = sd + TT * N;
-    float* skc = sb + TT;
-    float* su = skc + TT;
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
+}
 
-    float st[NT];
+// One state matrix per head; a thread keeps NT_ state entries of one value channel, JP lanes share the channel (lane j owns
+// the 4-entry groups j, j + JP, ...: neighbouring lanes read neighbouring 16-byte pieces of shared memory). The prepared
+// operands of TT tokens at a time are copied into one of two shared-memory buffers with cp.async while the tokens of the
+// other buffer run, so the sequential loop reads only shared memory and registers. Per token: the state decays, the JP lanes
+// reduce St^T k and St^T q together, the write w = beta (v - St^T k) lands, and the read-out is St^T q + (k . q) w: the same
+// value as reading the state after the write, with one reduction round instead of two. Shared rows are padded to JP * NT_
+// entries and the padding stays zero, so the inner loops need no bounds.
+template <int NT_>
+__global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(DeltaScanArgs a, SeqPos pos) {
+    if (seq_done(pos)) return;
+    extern __shared__ __align__(16) float sm[];
+    const int N = a.N, P = a.P, S = a.S, TTn = a.TT;
+    const int JP = blockDim.x, cols = blockDim.y;
+    const int h = blockIdx.x, col = threadIdx.y, j = threadIdx.x;
+    const int p0 = blockIdx.y * cols, p = p0 + col;
+    const int tid = threadIdx.y * JP + threadIdx.x, nthr = cols * JP;
+    const int NP = JP * NT_;
+    const int g = h / (a.H / a.G);
+    const DeltaOperands o = delta_operands(const_cast<float*>(a.ops), a.T, a.H, a.G, N, P);
+    const float* gk = o.k + ((size_t)g * a.T + a.r0) * N;
+    const float* gq = o.q + ((size_t)g * a.T + a.r0) * N;
+    const float* gd = a.dec + ((size_t)h * a.T + a.r0) * N;
+    const float* gv = o.v + ((size_t)h * a.T + a.r0) * P + p0;
+    const float* gb = o.beta + (size_t)h * a.T + a.r0;
+    const float* gkq = o.kq + (size_t)g * a.T + a.r0;
+    // one buffer: k[TT][NP], q[TT][NP], d[TT][NP], u[TT][cols], beta[TT], kq[TT]
+    const int buf_floats = TTn * (3 * NP + cols + 2);
+    for (int e = tid; e < 2 * buf_floats; e += nthr) sm[e] = 0.f;
+    __syncthreads();
+
+    float st[NT_];
     float* gstate = a.state + ((size_t)h * P + (p < P ? p : 0)) * N;
 #pragma unroll
-    for (int i = 0; i < NT; ++i) st[i] = (p < P && n0 + i < N) ? gstate[n0 + i] : 0.f;
-    const T* gk = (const T*)a.k + (size_t)g * N;
-    const T* gc = (const T*)a.c + (size_t)g * N;
-    const T* gu = (const T*)a.u + (size_t)h * P + blockIdx.y * cols;
+    for (int i = 0; i < NT_; ++i) {
+        const int n = ((i >> 2) * JP + j) * 4 + (i & 3);
+        st[i] = (p < P && n < N) ? gstate[n] : 0.f;
+    }
 
-    for (int t0 = 0; t0 < S; t0 += TT) {
-        const int nt = min(TT, S - t0);
-        __syncthreads();
-        for (int e = tid; e < nt * N; e += nthr) {
-            const int t = e / N, n = e % N;
-            sk[e] = ldf(gk + (size_t)(t0 + t) * a.ld_k + n);
-            scv[e] = ldf(gc + (size_t)(t0 + t) * a.ld_c + n);
-            sd[e] = expf(a.a[((size_t)(t0 + t) * a.heads + h) * N + n]);
+    auto fill = [&](int b, int t0) {
+        float* sk = sm + b * buf_floats;
+        float* sq = sk + TTn * NP;
+        float* sd = sq + TTn * NP;
+        float* su = sd + TTn * NP;
+        float* sb = su + TTn * cols;
+        float* skq = sb + TTn;
+        const int nt = min(TTn, S - t0);
+        if (a.async && NP == N) {               // whole rows: the stage's operands are three contiguous spans
+            const float* ck = gk + (size_t)t0 * N;
+            const float* cq = gq + (size_t)t0 * N;
+            const float* cd = gd + (size_t)t0 * N;
+            for (int e = tid * 4; e < nt * N; e += nthr * 4) {
+                cp_async16(sk + e, ck + e, true);
+                cp_async16(sq + e, cq + e, true);
+                cp_async16(sd + e, cd + e, true);
+            }
+        } else if (a.async) {
+            const int ch = N >> 2;
+            for (int e = tid; e < nt * ch; e += nthr) {
+                const int t = e / ch, c = (e % ch) << 2;
+                cp_async16(sk + t * NP + c, gk + (size_t)(t0 + t) * N + c, true);
+                cp_async16(sq + t * NP + c, gq + (size_t)(t0 + t) * N + c, true);
+                cp_async16(sd + t * NP + c, gd + (size_t)(t0 + t) * N + c, true);
+            }
+        } else {
+            for (int e = tid; e < nt * N; e += nthr) {
+                const int t = e / N, n = e % N;
+                sk[t * NP + n] = gk[(size_t)(t0 + t) * N + n];
+                sq[t * NP + n] = gq[(size_t)(t0 + t) * N + n];
+                sd[t * NP + n] = gd[(size_t)(t0 + t) * N + n];
+            }
         }
-        for (int e = tid; e < nt; e += nthr) sb[e] = a.sc ? a.sc[(size_t)(t0 + e) * a.heads + h] : 1.f;
         for (int e = tid; e < nt * cols; e += nthr) {
             const int t = e / cols, c = e % cols;
-            su[e] = (blockIdx.y * cols + c < P) ? ldf(gu + (size_t)(t0 + t) * a.ld_u + c) : 0.f;
+            if (p0 + c < P) cp_async4(su + e, gv + (size_t)(t0 + t) * P + c);
         }
-        __syncthreads();
-        for (int t = tid >> 5; t < nt; t += nthr >> 5) {     // one warp per token: unit length, scale, k . c
-            const int lane = tid & 31;
-            float sk2 = 0.f, sc2 = 0.f;
-            for (int n = lane; n < N; n += 32) { sk2 = fmaf(sk[t * N + n], sk[t * N + n], sk2); sc2 = fmaf(scv[t * N + n], scv[t * N + n], sc2); }
-            sk2 = warp_sum(sk2); sc2 = warp_sum(sc2);
-            const float rk = a.unit_eps > 0.f ? 1.f / sqrtf(sk2 + a.unit_eps) : 1.f;
-            const float rc = (a.unit_eps > 0.f ? 1.f / sqrtf(sc2 + a.unit_eps) : 1.f) * a.cs;
-            float kc = 0.f;
-            for (int n = lane; n < N; n += 32) {
-                const float kv = sk[t * N + n] * rk, cv = scv[t * N + n] * rc;
-                sk[t * N + n] = kv; scv[t * N + n] = cv;
-                kc = fmaf(kv, cv, kc);
-            }
-            kc = warp_sum(kc);
-            if (lane == 0) skc[t] = kc;
+        for (int t = tid; t < nt; t += nthr) {
+            cp_async4(sb + t, gb + t0 + t);
+            cp_async4(skq + t, gkq + t0 + t);
         }
-        __syncthreads();
+        cp_async_commit();
+    };
+
+    fill(0, 0);
+    int b = 0;
+    for (int t0 = 0; t0 < S; t0 += TTn, b ^= 1) {
+        cp_async_wait<0>();
+        __syncthreads();            // buffer b is complete, and every thread has left buffer b ^ 1
+        if (t0 + TTn < S) fill(b ^ 1, t0 + TTn);
+        const float* sk = sm + b * buf_floats;
+        const float* sq = sk + TTn * NP;
+        const float* sd = sq + TTn * NP;
+        const float* su = sd + TTn * NP + col;
+        const float* sb = sd + TTn * NP + TTn * cols;
+        const float* skq = sb + TTn;
+        const int nt = min(TTn, S - t0);
+        float* yo = a.y + (size_t)t0 * a.ld_y + (size_t)h * P + p;
+#pragma unroll 4
         for (int t = 0; t < nt; ++t) {
-            const float u = su[t * cols + col];
-            const float* kt = sk + t * N + n0;
-            const float* ct = scv + t * N + n0;
-            const float* dv = sd + t * N + n0;
-            float ks = 0.f, cs = 0.f;
+            const float4* k4 = reinterpret_cast<const float4*>(sk + t * NP) + j;
+            const float4* q4 = reinterpret_cast<const float4*>(sq + t * NP) + j;
+            const float4* d4 = reinterpret_cast<const float4*>(sd + t * NP) + j;
+            float kv[NT_];
+            float ks[NT_ / 4], qs[NT_ / 4];
 #pragma unroll
-            for (int i = 0; i < NT; ++i) {
-                if (n0 + i < N) {
-                    st[i] *= dv[i];
-                    ks = fmaf(st[i], kt[i], ks);
-                    cs = fmaf(st[i], ct[i], cs);
-                }
+            for (int i = 0; i < NT_ / 4; ++i) {
+                const float4 kk = k4[i * JP], qq = q4[i * JP], dd = d4[i * JP];
+                kv[4 * i] = kk.x; kv[4 * i + 1] = kk.y; kv[4 * i + 2] = kk.z; kv[4 * i + 3] = kk.w;
+                st[4 * i] *= dd.x; st[4 * i + 1] *= dd.y; st[4 * i + 2] *= dd.z; st[4 * i + 3] *= dd.w;
+                ks[i] = fmaf(st[4 * i + 3], kk.w, fmaf(st[4 * i + 2], kk.z, fmaf(st[4 * i + 1], kk.y, st[4 * i] * kk.x)));
+                qs[i] = fmaf(st[4 * i + 3], qq.w, fmaf(st[4 * i + 2], qq.z, fmaf(st[4 * i + 1], qq.y, st[4 * i] * qq.x)));
             }
-            for (int o = JP >> 1; o > 0; o >>= 1) {          // fixed butterfly order
-                ks += __shfl_xor_sync(0xffffffffu, ks, o);
-                cs += __shfl_xor_sync(0xffffffffu, cs, o);
-            }
-            const float w = sb[t] * (u - ks);
+            float ksum = ks[0], qsum = qs[0];
 #pragma unroll
-            for (int i = 0; i < NT; ++i)
-                if (n0 + i < N) st[i] = fmaf(kt[i], w, st[i]);
-            if (j == 0 && p < P) a.y[(size_t)(t0 + t) * a.ld_y + (size_t)h * P + p] = fmaf(skc[t], w, cs);
+            for (int i = 1; i < NT_ / 4; ++i) { ksum += ks[i]; qsum += qs[i]; }
+            for (int o2 = JP >> 1; o2 > 0; o2 >>= 1) {          // fixed butterfly order
+                ksum += __shfl_xor_sync(0xffffffffu, ksum, o2);
+                qsum += __shfl_xor_sync(0xffffffffu, qsum, o2);
+            }
+            const float w = sb[t] * (su[t * cols] - ksum);
+#pragma unroll
+            for (int i = 0; i < NT_; ++i) st[i] = fmaf(kv[i], w, st[i]);
+            if (j == 0 && p < P) yo[(size_t)t * a.ld_y] = fmaf(skq[t], w, qsum);
         }
     }
     if (p < P) {
 #pragma unroll
-        for (int i = 0; i < NT; ++i)
-            if (n0 + i < N) gstate[n0 + i] = st[i];
+        for (int i = 0; i < NT_; ++i) {
+            const int n = ((i >> 2) * JP + j) * 4 + (i & 3);
+            if (n < N) gstate[n] = st[i];
+        }
     }
 }
 
@@ -351,15 +421,46 @@ int causal_conv(int dt, const void* in, int ld_in, void* out, int ld_out, const 
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }
 
-int delta_gates(int dt, float* z, const float* dt_bias, const float* a_log, const void* b, int ld_b, float* beta_out, int S,
-                int heads, int N, cudaStream_t s) {
-    if (!z || !dt_bias || !a_log || !b || !beta_out || S < 1 || heads < 1 || N < 1) return -2;
-    const int64_t n = (int64_t)S * heads * N;
+int delta_pack(int dt, const DeltaPackArgs& a, cudaStream_t s) {
+    if (!a.qkv || !a.z || !a.dt_bias || !a.a_log || !a.b || !a.out || !a.dec || a.S < 1 || a.H < 1 || a.G < 1 || a.H % a.G || a.N < 1 ||
+        a.P < 1)
+        return -2;
+    const int warps = a.S * a.G;
     count_launch();
-    if (dt == DT_F32)
-        delta_gates_kernel<float><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(z, dt_bias, a_log, (const float*)b, ld_b, beta_out, S, heads, N);
-    else
-        delta_gates_kernel<bf16><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(z, dt_bias, a_log, (const bf16*)b, ld_b, beta_out, S, heads, N);
+    if (dt == DT_F32) delta_pack_kernel<float><<<(warps + 3) / 4, 128, 0, s>>>(a);
+    else delta_pack_kernel<bf16><<<(warps + 3) / 4, 128, 0, s>>>(a);
+    return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}
+
+int delta_scan(const DeltaScanArgs& q, SeqPos pos, cudaStream_t s) {
+    if (!q.ops || !q.dec || !q.state || !q.y || q.S < 1 || q.T < q.S || q.r0 < 0 || q.r0 + q.S > q.T || q.H < 1 || q.G < 1 || q.H % q.G ||
+        q.N < 1 || q.N > 512 || q.P < 1)
+        return -2;
+    DeltaScanArgs a = q;
+    // state entries per thread: 8 (16 lanes per value channel at 128 key channels) unless the key size needs 16
+    static int forced = -1;
+    if (forced < 0) { const char* e = getenv("LIVECC_B200_DELTA_NT"); forced = e ? atoi(e) : 0; }
+    int nt = a.N > 256 ? 16 : (a.N > 32 ? 8 : 4);
+    if ((forced == 4 || forced == 8 || forced == 16) && forced * 32 >= a.N) nt = forced;
+    int JP = 1;
+    while (JP * nt < a.N) JP *= 2;
+    int cols = kScanThreads / JP;
+    while (cols * JP > 32 && cols / 2 >= a.P) cols /= 2;   // narrow heads: fewer idle lanes, but always whole warps
+    const int NP = JP * nt;
+    a.TT = 16;
+    while (a.TT > 2 && (size_t)2 * a.TT * (3 * NP + cols + 2) * sizeof(float) > 64 * 1024) a.TT /= 2;
+    // 16-byte copies need 16-byte aligned rows in every operand block (each block starts at a multiple of 4 floats)
+    a.async = (a.N % 4) == 0 && ((uintptr_t)a.ops % 16) == 0 && ((uintptr_t)a.dec % 16) == 0;
+    const size_t smem = (size_t)2 * a.TT * (3 * NP + cols + 2) * sizeof(float);
+    dim3 block(JP, cols), grid(a.H, (a.P + cols - 1) / cols);
+    count_launch();
+#define LCC_DSCAN(NTV)                                                                                                          \
+    do {                                                                                                                        \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<NTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        delta_scan_kernel<NTV><<<grid, block, smem, s>>>(a, pos);                                                               \
+    } while (0)
+    if (nt == 4) LCC_DSCAN(4); else if (nt == 8) LCC_DSCAN(8); else LCC_DSCAN(16);
+#undef LCC_DSCAN
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }
 
@@ -397,28 +498,17 @@ int gated_scan(const ScanArgs& a, SeqPos pos, cudaStream_t s) {
     if (!a.k || !a.c || !a.u || !a.a || !a.state || !a.y || a.S < 1 || a.heads < 1 || a.N < 1 || a.P < 1 ||
         a.heads_per_group < 1)
         return -2;
-    if (a.delta && (!a.vec_decay || a.skip)) return -2;
-    if (!a.delta && a.ws && a.S >= kScanChunkedMin && !pos.kv_len) return gated_scan_chunked(a, pos, s);
+    if (a.ws && a.S >= kScanChunkedMin && !pos.kv_len) return gated_scan_chunked(a, pos, s);
     int JP = 1;
     while (JP * NT < a.N) JP *= 2;
     if (JP > 32) return -3;  // N <= 512
     int cols = kScanThreads / JP;
     while (cols * JP > 32 && cols / 2 >= a.P) cols /= 2;   // narrow heads: fewer idle lanes, but always whole warps
     dim3 block(JP, cols), grid(a.heads, (a.P + cols - 1) / cols);
-    const size_t smem = sizeof(float) * ((size_t)TT * a.N * 2 + (size_t)TT * (a.vec_decay ? a.N : 1) + TT * (a.delta ? 2 : 1) +
+    const size_t smem = sizeof(float) * ((size_t)TT * a.N * 2 + (size_t)TT * (a.vec_decay ? a.N : 1) + TT +
                                          (size_t)TT * cols);
     if (smem > 200 * 1024) return -3;
     count_launch();
-    if (a.delta) {
-        if (a.dt == DT_F32) {
-            if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            delta_scan_kernel<float><<<grid, block, smem, s>>>(a, pos);
-        } else {
-            if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            delta_scan_kernel<bf16><<<grid, block, smem, s>>>(a, pos);
-        }
-        return cudaGetLastError() == cudaSuccess ? 0 : -100;
-    }
 #define LCC_SCAN(T, V)                                                                                            \
     do {                                                                                                          \
         if (smem > 48 * 1024) cudaFuncSetAttribute(gated_scan_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \

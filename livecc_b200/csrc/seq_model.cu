@@ -123,6 +123,8 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
         if (l.type == LCC_MIX_DELTA) {
             wp = std::max(wp, z.d_proj); wm = std::max(wm, std::max(z.d_conv_ch, ld8(z.d_nv))); wp2 = std::max(wp2, ld8(z.d_nv));
             wy = std::max(wy, z.d_nv); wf = std::max(wf, l.d_heads * l.d_dim);
+            // (the head-by-head operand blocks are each padded to 4 floats: up to 5 x 4 more floats in all than rows x width)
+            wq = std::max(wq, 2 * z.d_nk + z.d_nv + l.d_kv_heads + l.d_heads + 24);
         }
         if (l.type == LCC_MIX_LATENT && l.a_q_rank > 0) { wp2 = std::max(wp2, ld8(z.a_nq)); wm = std::max(wm, ld8(l.a_q_rank)); }
         if (l.type == LCC_MIX_ATTENTION && l.m_vmix_role == 1) wvk = std::max(wvk, ld8(z.m_nv));
@@ -506,36 +508,35 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
             }
         }
         if (l.type == LCC_MIX_DELTA) {
-            // [q | k | v | beta | decay-down | gate-down] -> causal convolution + silu on q, k, v -> decay-up (fp32) -> log decays
-            // and beta -> delta rule (unit q, k inside) -> gate-up -> unit-rms heads x weight x sigmoid(gate) -> out-proj
+            // [q | k | v | beta | decay-down | gate-down] -> causal convolution + silu on q, k, v -> decay-up (fp32) -> the
+            // recurrence's operands in fp32 (unit q and k, decays, beta) -> delta rule -> gate-up -> unit-rms heads x weight x
+            // sigmoid(gate) -> out-proj
             const int ldp = z.d_proj, ldm = z.d_conv_ch, H = l.d_heads, HN = H * l.d_dim, ldv = ld8(z.d_nv);
             STEP(linear(m, xa, W, l.d_in, nullptr, proj, ldp, false, T, z.d_proj, W, s), "delta-rule in-proj");
             STEP(linear(m, proj + (size_t)z.d_a1 * es, ldp, l.d_a_up, nullptr, f1, HN, true, T, HN, l.d_rank_a, s), "decay projection");
-            STEP(lcc::delta_gates(dt, f1, l.d_dt_bias_f32, l.d_a_log_f32, proj + (size_t)z.d_b * es, ldp, f2, T, H, l.d_dim, s), "decays and write strengths");
             STEP(linear(m, proj + (size_t)z.d_g1 * es, ldp, l.d_g_up, nullptr, proj2, ldv, false, T, z.d_nv, l.d_rank_g, s), "gate projection");
             int r0 = 0;
             for (int e = 0; e < n_entries; ++e) {
                 const lcc_seq_entry& en = entries[e];
                 float* st = en.layer_state[li];
                 if (!st) LCC_FAIL(m->ctx, -2, "lcc_seq_forward: entry %d has no state for layer %d", e, li);
-                st += st_off;
-                const lcc::SeqPos pos = pos_of(en);
-                uint8_t* qkv = mid + (size_t)r0 * ldm * es;
-                STEP(lcc::causal_conv(dt, proj + (size_t)r0 * ldp * es, ldp, qkv, ldm, l.d_conv_w_f32, nullptr, st, en.n_new, z.d_conv_ch,
-                                      l.d_conv, pos, s, lcc::ConvOpts{false, true, false}), "causal convolution");
-                lcc::ScanArgs a{};
-                a.dt = dt;
-                a.k = qkv + (size_t)z.d_k * es; a.ld_k = ldm;
-                a.c = qkv; a.ld_c = ldm;
-                a.u = qkv + (size_t)z.d_v * es; a.ld_u = ldm;
-                a.a = f1 + (size_t)r0 * HN; a.vec_decay = 1;
-                a.sc = f2 + (size_t)r0 * H; a.skip = nullptr; a.cs = 1.f / sqrtf((float)l.d_dim);
-                a.state = st + (size_t)z.d_conv_ch * (l.d_conv - 1);
+                STEP(lcc::causal_conv(dt, proj + (size_t)r0 * ldp * es, ldp, mid + (size_t)r0 * ldm * es, ldm, l.d_conv_w_f32, nullptr, st + st_off,
+                                      en.n_new, z.d_conv_ch, l.d_conv, pos_of(en), s, lcc::ConvOpts{false, true, false}), "causal convolution");
+                r0 += en.n_new;
+            }
+            // unit q and k, k . q, fp32 values, decays and write strengths of all rows, head by head (operands in q32, decays in f2)
+            lcc::DeltaPackArgs pa{mid, ldm, z.d_k, z.d_v, f1, l.d_dt_bias_f32, l.d_a_log_f32, proj + (size_t)z.d_b * es, ldp, q32, f2,
+                                  T, H, l.d_kv_heads, l.d_dim, l.d_vdim, 1e-6f, 1.f / sqrtf((float)l.d_dim)};
+            STEP(lcc::delta_pack(dt, pa, s), "delta-rule operands");
+            r0 = 0;
+            for (int e = 0; e < n_entries; ++e) {
+                const lcc_seq_entry& en = entries[e];
+                lcc::DeltaScanArgs a{};
+                a.ops = q32; a.dec = f2; a.T = T; a.r0 = r0;
+                a.state = en.layer_state[li] + st_off + (size_t)z.d_conv_ch * (l.d_conv - 1);
                 a.y = y32 + (size_t)r0 * z.d_nv; a.ld_y = z.d_nv;
-                a.S = en.n_new; a.heads = H; a.heads_per_group = H / l.d_kv_heads; a.N = l.d_dim; a.P = l.d_vdim;
-                a.ws = nullptr; a.ws_floats = 0;
-                a.delta = true; a.unit_eps = 1e-6f;
-                STEP(lcc::gated_scan(a, pos, s), "delta-rule recurrence");
+                a.S = en.n_new; a.H = H; a.G = l.d_kv_heads; a.N = l.d_dim; a.P = l.d_vdim;
+                STEP(lcc::delta_scan(a, pos_of(en), s), "delta-rule recurrence");
                 r0 += en.n_new;
             }
             STEP(lcc::gated_group_norm(dt, y32, z.d_nv, proj2, ldv, l.d_norm_f32, l.d_vdim, mid2, ldv, T, z.d_nv, l.d_vdim, 2, d.eps, s),

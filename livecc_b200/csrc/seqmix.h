@@ -87,10 +87,49 @@ int ssm_step_decay(int dt, const void* raw, int ld, const float* dt_bias, const 
 // Per-channel log decays of gated linear attention: log(sigmoid(z + bias)) / tau; z: [S, n] slice (storage dt).
 int gla_decay(int dt, const void* z, int ld, const float* bias, float tau, float* decay_out, int S, int n,
               cudaStream_t s);
-// Gates of a delta-rule layer with a decay per key channel: z fp32 [S, heads*N] is replaced by the log decay
-// -exp(a_log[h]) * softplus(z + dt_bias[h*N + n]); beta_out fp32 [S, heads] = sigmoid(b), b: [S, heads] slice (storage dt).
-int delta_gates(int dt, float* z, const float* dt_bias, const float* a_log, const void* b, int ld_b, float* beta_out, int S,
-                int heads, int N, cudaStream_t s);
+// Gated delta rule with a decay per head and key channel, one state matrix St[n, p] per head (H value heads of P channels over
+// G key heads of N channels, head h reads key head h / (H / G)):
+//     St <- diag(d_t) St;  w = beta_t (v_t - St^T k_t);  St <- St + k_t w^T;  y_t = St^T q_t
+// in two steps. delta_pack prepares all S rows of a step at once: qkv [S, ld] (storage dt) holds q at column 0, k at col_k and
+// v at col_v; k and q are divided by sqrt(sum(x^2) + unit_eps) per key head (unit_eps <= 0: left as they are), q also times
+// q_scale. The prepared operands are fp32 and laid out head by head (the rows of one head contiguous):
+//     out: k [G][S][N] | q [G][S][N] | v [H][S][P] | k . q [G][S] | beta [H][S]   (every block padded to a multiple of 4 floats)
+//     dec: [H][S][N] = exp(-exp(a_log[h]) * softplus(z + dt_bias[h*N + n])), z: fp32 [S, H*N]
+// beta = sigmoid(b), b: [S, H] slice (storage dt).
+struct DeltaOperands { float *k, *q, *v, *kq, *beta; };
+__host__ __device__ inline size_t delta_pad4(size_t n) { return (n + 3) / 4 * 4; }
+__host__ __device__ inline DeltaOperands delta_operands(float* base, int S, int H, int G, int N, int P) {
+    DeltaOperands o;
+    o.k = base;
+    o.q = o.k + delta_pad4((size_t)G * S * N);
+    o.v = o.q + delta_pad4((size_t)G * S * N);
+    o.kq = o.v + delta_pad4((size_t)H * S * P);
+    o.beta = o.kq + delta_pad4((size_t)G * S);
+    return o;
+}
+inline size_t delta_operand_floats(int S, int H, int G, int N, int P) {
+    return 2 * delta_pad4((size_t)G * S * N) + delta_pad4((size_t)H * S * P) + delta_pad4((size_t)G * S) + delta_pad4((size_t)H * S);
+}
+struct DeltaPackArgs {
+    const void* qkv; int ld, col_k, col_v;
+    const float* z; const float* dt_bias; const float* a_log;
+    const void* b; int ld_b;
+    float* out; float* dec;
+    int S, H, G, N, P;
+    float unit_eps, q_scale;
+};
+int delta_pack(int dt, const DeltaPackArgs& a, cudaStream_t s);
+// delta_scan runs the recurrence token by token over one sequence's S rows (prompt portions and decode steps alike): rows
+// r0 .. r0 + S - 1 of the T rows that delta_pack prepared (ops = its `out`). state: fp32 [H, P, N] (n fastest), read at the start
+// and written back at the end; y: fp32 [S, H*P]. TT and async are chosen by the launcher.
+struct DeltaScanArgs {
+    const float* ops; const float* dec;
+    int T, r0;
+    float* state; float* y; int ld_y;
+    int S, H, G, N, P;
+    int TT; bool async;
+};
+int delta_scan(const DeltaScanArgs& a, SeqPos pos, cudaStream_t s);
 
 // Gated linear recurrence, one state matrix St[n, p] (n < N key channels, p < P value channels) per head:
 //     St <- diag(a_t) St + k_t (sc_t * u_t)^T ,   y_t = St^T (cs * c_t) + skip[h] * u_t
@@ -113,11 +152,6 @@ struct ScanArgs {
     float* y; int ld_y;
     int S, heads, heads_per_group, N, P;
     float* ws; size_t ws_floats;   // workspace of the sequence-parallel form (null: token by token)
-    // delta: the delta rule instead of the plain write (token by token in every call; sc is then the write strength beta and
-    // there is no skip term):  St <- diag(a_t) St;  w = sc_t (u_t - St^T k_t);  St <- St + k_t w^T;  y_t = St^T (cs c_t)
-    // unit_eps > 0: k_t and c_t are first divided by sqrt(sum(x^2) + unit_eps) per head (unit vectors)
-    bool delta = false;
-    float unit_eps = 0.f;
 };
 constexpr int kScanChunkedMin = 32;     // rows from which the sequence-parallel form runs
 constexpr int kScanMaxBlocks = 64;      // blocks of 64 rows per pass of the sequence-parallel form (bounds its workspace)

@@ -82,6 +82,32 @@ def dibedra_config(width: int, n_layers: int, ff: int, window: int, vocab: int =
                                      "logit_scale": 0.5})
 
 
+def lugizen_config(width: int, n_layers: int, ff: int, window: int, vocab: int = 32768) -> SeqModelConfig:
+    """Sublayers normed on their output behind a 4-tap convolution over time; layers in the pattern delta rule, delta rule,
+    attention, latent attention. Delta rule: width/128 heads of 128 key and 128 value channels, 4-tap q/k/v convolutions,
+    decay and gate bottlenecks of 64 channels. Attention: 128-channel heads, 8 query heads per key/value head, the first 64
+    channels rotated, values mixed across the attention layers. Latent attention: 128 + 64 channel query heads through a query
+    latent of 3/8 width, 192 latent + 64 rotary cache channels per token, 128-channel values, a window of `window` positions.
+    The first layer has a two-matrix feed-forward of width 3 ff / 2, every other layer 16 gated experts of width ff/4, 4 per
+    token: every token reads 3 x width x ff feed-forward weights, the dense gated `ff` of the models beside it."""
+    heads, layers = width // 128, []
+    moe = {"kind": "moe", "expert": {"ff": ff // 4 // 16 * 16}, "router": {"experts": 16, "top": 4}}
+    for i in range(n_layers):
+        k = i % 4
+        if k < 2:
+            L = {"type": "channel_delta", "mixer": dict(heads=heads, kv_heads=heads, dim=128, vdim=128, conv=4, decay_rank=64, gate_rank=64)}
+        elif k == 2:
+            L = {"type": "attention", "mixer": dict(heads=heads, kv_heads=max(1, heads // 8), dim=128, vdim=128, rot={"dims": 64, "base": 10000.0},
+                                                    scale=128 ** -0.5, v_mix=True)}
+        else:
+            L = {"type": "latent_attention", "mixer": dict(heads=heads, dim=128, rot_dim=64, vdim=128, kv_rank=192, q_rank=3 * width // 8,
+                                                           mask={"size": window}, rot={"dims": 64, "base": 10000.0}, scale=192 ** -0.5)}
+        L["mlp"] = {"kind": "dense", "ff": 3 * ff // 2 // 8 * 8} if i == 0 else moe
+        layers.append(L)
+    return SeqModelConfig.from_json({"architecture": "Lugizen", "vocab": vocab, "width": width, "layers": layers, "norm": {"eps": 1e-6},
+                                     "canon": {"taps": 4}})
+
+
 def qwen_config(width: int, n_layers: int, ff: int, vocab: int = 32768) -> LiveCCConfig:
     heads = width // 128
     return LiveCCConfig(
@@ -149,9 +175,10 @@ def run(sizes: List[str], prompt_lens: List[int], new_tokens: int, steps: int, w
     for name in sizes:
         width, n_layers, ff, chunk = SIZES[name]
         rec = {}
-        arms = {"Bimopel": ["bimopel"], "Kedelorn": ["kedelorn", "bimopel"], "Dibedra": ["dibedra", "kedelorn"]}[design]
+        arms = {"Bimopel": ["bimopel"], "Kedelorn": ["kedelorn", "bimopel"], "Dibedra": ["dibedra", "kedelorn"],
+                "Lugizen": ["lugizen", "kedelorn"]}[design]
         make = {"bimopel": lambda: seq_config(width, n_layers, ff, chunk), "kedelorn": lambda: kedelorn_config(width, n_layers, ff),
-                "dibedra": lambda: dibedra_config(width, n_layers, ff, chunk)}
+                "dibedra": lambda: dibedra_config(width, n_layers, ff, chunk), "lugizen": lambda: lugizen_config(width, n_layers, ff, chunk)}
         for label, cfg in [(a, make[a]()) for a in arms]:
             m = SeqLMForCausalLM.from_state_dict(cfg, synthetic_seq_tensors(cfg, seed=7, device="cuda"), dtype,
                                                  max_tokens=max(prompt_lens) + new_tokens + 64)
@@ -174,7 +201,7 @@ def run(sizes: List[str], prompt_lens: List[int], new_tokens: int, steps: int, w
 
 
 def main(args, design: str = "Bimopel") -> Dict:
-    """bench.py --arch seq | kedelorn | dibedra: one JSON line; `value` = decode tokens/s of the first size at the first prompt length."""
+    """bench.py --arch seq | kedelorn | dibedra | lugizen: one JSON line; `value` = decode tokens/s of the first size at the first prompt length."""
     sizes = [s for s in (args.seq_sizes.split(",") if args.seq_sizes else list(SIZES)) if s in SIZES]
     lens = [int(x) for x in args.seq_prompt.split(",")]
     res = run(sizes, lens, args.max_new_tokens if args.max_new_tokens > 16 else 64, args.steps, max(args.warmup, 3), design=design)
@@ -182,7 +209,7 @@ def main(args, design: str = "Bimopel") -> Dict:
     return {"metric": "decode_tokens_per_s", "value": first["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": first["decode_ms_per_token"], "higher_is_better": True, "dtype": "bf16",
             "data": "synthetic (random weights, random ids)", "vs_baseline": None,
-            "config": {"model": f"{design} {sizes[0]} beside " + {"Kedelorn": "Bimopel and the ", "Dibedra": "Kedelorn and the "}.get(design, "") +
+            "config": {"model": f"{design} {sizes[0]} beside " + {"Kedelorn": "Bimopel and the ", "Dibedra": "Kedelorn and the ", "Lugizen": "Kedelorn and the "}.get(design, "") +
                                 "Qwen2-style decoder of equal width/depth/ff", "global_batch": 1,
                        "seq_len": lens[0], "parallelism": "1 gpu", "l2": "weights of every size exceed L2"},
             "sizes": res}

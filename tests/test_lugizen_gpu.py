@@ -62,6 +62,14 @@ def rows_rel(got, want):
     return (got - want).pow(2).mean(-1).sqrt() / want.pow(2).mean(-1).sqrt().clamp_min(1e-30)
 
 
+def close32(got, want):
+    """fp32 storage against the oracle: every row within the tolerance, but for the few rows (at most 2 in 100) in which a
+    sublayer's output nearly cancels: the norm behind the sublayer scales such a row up, rounding included, and plain fp32
+    arithmetic moves it by more than the product does. Those stay within ten times the tolerance."""
+    e = rows_rel(got, want)
+    return float(e.max()) < 10 * F32_TOL and float((e > F32_TOL).double().mean()) <= 0.02
+
+
 def bf16_ok(got, want, routed=False):
     """bf16 storage: the bulk of the rows stays within bf16 rounding and few rows lie beyond twice that. routed: a stack with
     routers. A router logit close to the next one can fall the other way under rounding; the norm behind the feed-forward then
@@ -102,8 +110,8 @@ def test_whole_prompt_every_layer_matches_the_oracle_fp32(name):
     lg, dump = m.forward_step([(c, toks)], [list(range(len(toks)))], layer_dump=True)
     c.release()
     for li in range(len(d["layers"])):
-        assert rel(dump[li], want_layers[li]) < F32_TOL, f"residual stream after layer {li}"
-    assert rel(lg, want_lg) < F32_TOL
+        assert close32(dump[li], want_layers[li]), f"residual stream after layer {li}"
+    assert close32(lg, want_lg)
 
 
 @pytest.mark.parametrize("name", ["delta_only", "attention_only", "latent_only", "dense", "mixed", "odd"])
@@ -128,7 +136,7 @@ def test_each_mechanism_shows_in_these_weights(name, what):
     m, d, _ = model_of(name)
     toks = K.tokens(75, d["vocab"])
     got = run(m, toks, [])
-    assert rel(got, oracle(name, toks)[0]) < F32_TOL
+    assert close32(got, oracle(name, toks)[0])
     assert rel(got, oracle(name, toks, leave_out=(what,))[0]) > 100 * F32_TOL
 
 
@@ -151,10 +159,7 @@ def test_random_configurations_in_three_schedules(seed):
         portions.append(min(p, T - 20))
     m = build(d, tensors)
     for cuts in ([], [T - 20] + list(range(T - 19, T)), portions + list(range(T - 19, T))):
-        # (a sublayer whose output nearly cancels is scaled up by the norm behind it, rounding included: plain fp32 arithmetic
-        # shows the same rows; they are few and stay within ten times the tolerance)
-        e = rows_rel(run(m, toks, cuts), want)
-        assert float(e.max()) < 10 * F32_TOL and float((e > F32_TOL).double().mean()) <= 0.02
+        assert close32(run(m, toks, cuts), want)
     got = run(build(d, tensors, "bfloat16"), toks, portions)
     assert bool(torch.isfinite(got).all())
     if len(d["layers"]) <= 3:
