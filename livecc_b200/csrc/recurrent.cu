@@ -285,12 +285,13 @@ __global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(DeltaScanArgs 
     for (int e = tid; e < 2 * buf_floats; e += nthr) sm[e] = 0.f;
     __syncthreads();
 
-    float st[NT_];
+    float2 st[NT_ / 2];          // entry i of the thread is key channel ((i / 4) * JP + j) * 4 + i % 4
     float* gstate = a.state + ((size_t)h * P + (p < P ? p : 0)) * N;
 #pragma unroll
     for (int i = 0; i < NT_; ++i) {
         const int n = ((i >> 2) * JP + j) * 4 + (i & 3);
-        st[i] = (p < P && n < N) ? gstate[n] : 0.f;
+        const float v = (p < P && n < N) ? gstate[n] : 0.f;
+        if (i & 1) st[i >> 1].y = v; else st[i >> 1].x = v;
     }
 
     auto fill = [&](int b, int t0) {
@@ -356,26 +357,29 @@ __global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(DeltaScanArgs 
             const float4* k4 = reinterpret_cast<const float4*>(sk + t * NP) + j;
             const float4* q4 = reinterpret_cast<const float4*>(sq + t * NP) + j;
             const float4* d4 = reinterpret_cast<const float4*>(sd + t * NP) + j;
-            float kv[NT_];
-            float ks[NT_ / 4], qs[NT_ / 4];
+            // packed fp32 pairs (fma.rn.f32x2: each half rounds as a scalar fma does): half the arithmetic instructions
+            float2 kv[NT_ / 2];
+            float2 ks = make_float2(0.f, 0.f), qs = make_float2(0.f, 0.f);
 #pragma unroll
             for (int i = 0; i < NT_ / 4; ++i) {
                 const float4 kk = k4[i * JP], qq = q4[i * JP], dd = d4[i * JP];
-                kv[4 * i] = kk.x; kv[4 * i + 1] = kk.y; kv[4 * i + 2] = kk.z; kv[4 * i + 3] = kk.w;
-                st[4 * i] *= dd.x; st[4 * i + 1] *= dd.y; st[4 * i + 2] *= dd.z; st[4 * i + 3] *= dd.w;
-                ks[i] = fmaf(st[4 * i + 3], kk.w, fmaf(st[4 * i + 2], kk.z, fmaf(st[4 * i + 1], kk.y, st[4 * i] * kk.x)));
-                qs[i] = fmaf(st[4 * i + 3], qq.w, fmaf(st[4 * i + 2], qq.z, fmaf(st[4 * i + 1], qq.y, st[4 * i] * qq.x)));
+                kv[2 * i] = make_float2(kk.x, kk.y); kv[2 * i + 1] = make_float2(kk.z, kk.w);
+                st[2 * i] = __fmul2_rn(st[2 * i], make_float2(dd.x, dd.y));
+                st[2 * i + 1] = __fmul2_rn(st[2 * i + 1], make_float2(dd.z, dd.w));
+                ks = __ffma2_rn(st[2 * i], kv[2 * i], ks);
+                qs = __ffma2_rn(st[2 * i], make_float2(qq.x, qq.y), qs);
+                ks = __ffma2_rn(st[2 * i + 1], kv[2 * i + 1], ks);
+                qs = __ffma2_rn(st[2 * i + 1], make_float2(qq.z, qq.w), qs);
             }
-            float ksum = ks[0], qsum = qs[0];
-#pragma unroll
-            for (int i = 1; i < NT_ / 4; ++i) { ksum += ks[i]; qsum += qs[i]; }
+            float ksum = ks.x + ks.y, qsum = qs.x + qs.y;
             for (int o2 = JP >> 1; o2 > 0; o2 >>= 1) {          // fixed butterfly order
                 ksum += __shfl_xor_sync(0xffffffffu, ksum, o2);
                 qsum += __shfl_xor_sync(0xffffffffu, qsum, o2);
             }
             const float w = sb[t] * (su[t * cols] - ksum);
+            const float2 w2 = make_float2(w, w);
 #pragma unroll
-            for (int i = 0; i < NT_; ++i) st[i] = fmaf(kv[i], w, st[i]);
+            for (int i = 0; i < NT_ / 2; ++i) st[i] = __ffma2_rn(kv[i], w2, st[i]);
             if (j == 0 && p < P) yo[(size_t)t * a.ld_y] = fmaf(skq[t], w, qsum);
         }
     }
@@ -383,7 +387,7 @@ __global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(DeltaScanArgs 
 #pragma unroll
         for (int i = 0; i < NT_; ++i) {
             const int n = ((i >> 2) * JP + j) * 4 + (i & 3);
-            if (n < N) gstate[n] = st[i];
+            if (n < N) gstate[n] = (i & 1) ? st[i >> 1].y : st[i >> 1].x;
         }
     }
 }
@@ -437,10 +441,11 @@ int delta_scan(const DeltaScanArgs& q, SeqPos pos, cudaStream_t s) {
         q.N < 1 || q.N > 512 || q.P < 1)
         return -2;
     DeltaScanArgs a = q;
-    // state entries per thread: 8 (16 lanes per value channel at 128 key channels) unless the key size needs 16
+    // state entries per thread: 16 from 65 key channels on (8 lanes per value channel at 128: three shuffle rounds and the
+    // fewest instructions per token), fewer for narrow heads so that a channel still spreads over lanes
     static int forced = -1;
     if (forced < 0) { const char* e = getenv("LIVECC_B200_DELTA_NT"); forced = e ? atoi(e) : 0; }
-    int nt = a.N > 256 ? 16 : (a.N > 32 ? 8 : 4);
+    int nt = a.N > 64 ? 16 : (a.N > 16 ? 8 : 4);
     if ((forced == 4 || forced == 8 || forced == 16) && forced * 32 >= a.N) nt = forced;
     int JP = 1;
     while (JP * nt < a.N) JP *= 2;
