@@ -292,7 +292,7 @@ int lcc_resize_bicubic_aa_u8(lcc_ctx* ctx, const lcc_resize_plan* plan, const ui
                              lcc_stream_t stream);
 
 /* ---- hybrid sequence models: decoder-only language models whose layers mix tokens with a state-space recurrence, gated
- * linear attention, retention, chunk-local attention, latent attention or sliding-window attention. A layer is
+ * linear attention, retention, a gated delta rule, chunk-local attention, latent attention or sliding-window attention. A layer is
  *     x <- norm1(alpha * x + mixer(x)),  then (if it has a feed-forward)  x <- norm2(alpha * x + ff(x))       (post-norm)
  * or, in a model with LCC_BLOCK_PRENORM_HC, pre-norm sublayers on several residual streams (see LCC_BLOCK_PRENORM_HC),
  * or, with LCC_BLOCK_PARALLEL, x <- x + mixer(norm1(x)) + ff(norm1(x)),

@@ -361,15 +361,17 @@ __global__ void glu_clamp_swish_kernel(const T* __restrict__ gu, int ld, T* __re
 }
 
 // x <- x + rms(y) * w for one row per CTA, y = the sublayer's row or the routed feed-forward's weighted sum of expert rows. A
-// thread keeps its E columns of y in registers between the sum of squares and the update (E = 0: rows wider than 256 * 16
-// columns form y twice). Each column's sum runs in the same order for every S.
-template <typename T, int E>
+// thread keeps its E pieces of y in registers between the sum of squares and the update (E = 0: rows wider than 256 * 16
+// pieces form y twice); a piece is one column, or with VEC four neighbouring ones (one 16-byte / 8-byte access). Each
+// column's sum runs in the same order in both forms and for every S.
+template <typename T, int E, bool VEC>
 __global__ void __launch_bounds__(256) branch_norm_residual_kernel(float* __restrict__ x32, const T* __restrict__ a, int ld_a, bool has_mc,
                                                                    MoeCombine mc, const float* __restrict__ w, float eps,
                                                                    T* __restrict__ xa, int W) {
     __shared__ float red[32];
     __shared__ int spos[kCombineTop];
     __shared__ float swt[kCombineTop];
+    constexpr int V = VEC ? 4 : 1;
     const int r = blockIdx.x;
     float* x = x32 + (size_t)r * W;
     const int top = has_mc ? mc.top : 0;
@@ -382,48 +384,72 @@ __global__ void __launch_bounds__(256) branch_norm_residual_kernel(float* __rest
         __syncthreads();
     }
     const float gs = (has_mc && mc.so) ? mc.gate[r] : 0.f;
-    auto value = [&](int c) -> float {
-        if (!has_mc) return ldf(a + (size_t)r * ld_a + c);
-        float y = 0.f;
+    auto value = [&](int c, float (&y)[V]) {
+        float t[V];
+        if (!has_mc) {
+            if (VEC) ld4(a + (size_t)r * ld_a + c, (float(&)[4])y); else y[0] = ldf(a + (size_t)r * ld_a + c);
+            return;
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) y[i] = 0.f;
         for (int k = 0; k < top; ++k) {
             const int p = cached ? spos[k] : mc.pos[(size_t)r * top + k];
             if (p < 0) continue;
             const float wk = cached ? swt[k] : mc.weight[(size_t)r * top + k];
-            y = fmaf(wk, ldf((const T*)mc.eo + (size_t)p * mc.ld_eo + c), y);
+            const T* src = (const T*)mc.eo + (size_t)p * mc.ld_eo + c;
+            if (VEC) ld4(src, (float(&)[4])t); else t[0] = ldf(src);
+#pragma unroll
+            for (int i = 0; i < V; ++i) y[i] = fmaf(wk, t[i], y[i]);
         }
-        if (mc.so) y = fmaf(gs, ldf((const T*)mc.so + (size_t)r * mc.ld_so + c), y);
-        return y;
+        if (mc.so) {
+            const T* src = (const T*)mc.so + (size_t)r * mc.ld_so + c;
+            if (VEC) ld4(src, (float(&)[4])t); else t[0] = ldf(src);
+#pragma unroll
+            for (int i = 0; i < V; ++i) y[i] = fmaf(gs, t[i], y[i]);
+        }
+    };
+    auto update = [&](int c, const float (&y)[V], float rn) {
+        float v[V];
+        if (VEC) ld4(x + c, (float(&)[4])v); else v[0] = x[c];
+#pragma unroll
+        for (int i = 0; i < V; ++i) v[i] = fmaf(y[i] * rn, w[c + i], v[i]);
+        if (VEC) st4(x + c, (const float(&)[4])v); else x[c] = v[0];
+        if (xa) { if (VEC) st4(xa + (size_t)r * W + c, (const float(&)[4])v); else stf(xa + (size_t)r * W + c, v[0]); }
     };
     constexpr int EN = E > 0 ? E : 1;
-    float vy[EN];
+    float vy[EN][V];
     float ss = 0.f;
     if (E > 0) {
 #pragma unroll
         for (int i = 0; i < EN; ++i) {
-            const int c = threadIdx.x + i * 256;
-            vy[i] = c < W ? value(c) : 0.f;
-            ss = fmaf(vy[i], vy[i], ss);
+            const int c = (threadIdx.x + i * 256) * V;
+#pragma unroll
+            for (int u = 0; u < V; ++u) vy[i][u] = 0.f;
+            if (c < W) value(c, vy[i]);
+#pragma unroll
+            for (int u = 0; u < V; ++u) ss = fmaf(vy[i][u], vy[i][u], ss);
         }
     } else {
-        for (int c = threadIdx.x; c < W; c += 256) { const float y = value(c); ss = fmaf(y, y, ss); }
+        for (int c = threadIdx.x * V; c < W; c += 256 * V) {
+            float y[V];
+            value(c, y);
+#pragma unroll
+            for (int u = 0; u < V; ++u) ss = fmaf(y[u], y[u], ss);
+        }
     }
     ss = block_sum(ss, red);
     const float rn = 1.f / sqrtf(ss / (float)W + eps);
     if (E > 0) {
 #pragma unroll
         for (int i = 0; i < EN; ++i) {
-            const int c = threadIdx.x + i * 256;
-            if (c < W) {
-                const float v = fmaf(vy[i] * rn, w[c], x[c]);
-                x[c] = v;
-                if (xa) stf(xa + (size_t)r * W + c, v);
-            }
+            const int c = (threadIdx.x + i * 256) * V;
+            if (c < W) update(c, vy[i], rn);
         }
     } else {
-        for (int c = threadIdx.x; c < W; c += 256) {
-            const float v = fmaf(value(c) * rn, w[c], x[c]);
-            x[c] = v;
-            if (xa) stf(xa + (size_t)r * W + c, v);
+        for (int c = threadIdx.x * V; c < W; c += 256 * V) {
+            float y[V];
+            value(c, y);
+            update(c, y, rn);
         }
     }
 }
@@ -572,12 +598,17 @@ int branch_norm_residual(int dt, float* x32, const void* a, int ld_a, const MoeC
     if (mc && (!mc->eo || !mc->pos || !mc->weight || mc->top < 1 || (mc->so && !mc->gate))) return -2;
     count_launch();
     const MoeCombine m = mc ? *mc : MoeCombine{};
-#define LCC_BNR(E)                                                                                                             \
+    const size_t es = dt == DT_F32 ? 4 : 2;
+    auto ok4 = [&](const void* p, int ld) { return !p || ((ld % 4) == 0 && ((uintptr_t)p % (4 * es)) == 0); };
+    const bool vec = (W % 4) == 0 && ((uintptr_t)x32 % 16) == 0 && ((uintptr_t)w % 16) == 0 && ok4(a, ld_a) && ok4(xa, W) &&
+                     (!mc || (ok4(m.eo, m.ld_eo) && ok4(m.so, m.ld_so)));
+#define LCC_BNR2(E, VECB)                                                                                                      \
     do {                                                                                                                       \
-        if (dt == DT_F32) branch_norm_residual_kernel<float, E><<<S, 256, 0, s>>>(x32, (const float*)a, ld_a, mc != nullptr, m, w, eps, (float*)xa, W); \
-        else branch_norm_residual_kernel<bf16, E><<<S, 256, 0, s>>>(x32, (const bf16*)a, ld_a, mc != nullptr, m, w, eps, (bf16*)xa, W);                 \
+        if (dt == DT_F32) branch_norm_residual_kernel<float, E, VECB><<<S, 256, 0, s>>>(x32, (const float*)a, ld_a, mc != nullptr, m, w, eps, (float*)xa, W); \
+        else branch_norm_residual_kernel<bf16, E, VECB><<<S, 256, 0, s>>>(x32, (const bf16*)a, ld_a, mc != nullptr, m, w, eps, (bf16*)xa, W);                 \
     } while (0)
-    const int per = (W + 255) / 256;
+#define LCC_BNR(E) do { if (vec) LCC_BNR2(E, true); else LCC_BNR2(E, false); } while (0)
+    const int per = (W / (vec ? 4 : 1) + 255) / 256;      // pieces per thread: the form depends on the row's width alone
     if (per <= 1) LCC_BNR(1);
     else if (per <= 2) LCC_BNR(2);
     else if (per <= 4) LCC_BNR(4);
@@ -585,6 +616,7 @@ int branch_norm_residual(int dt, float* x32, const void* a, int ld_a, const MoeC
     else if (per <= kRowCache) LCC_BNR(16);
     else LCC_BNR(0);
 #undef LCC_BNR
+#undef LCC_BNR2
     return done();
 }
 

@@ -1,13 +1,13 @@
 // Internal launch interfaces of the sequence-mixing ops used by the hybrid decoder models (state-space layers, gated
 // linear attention, chunk-local attention with a softmax sink, post-norm residual blocks):
 //   linear_any.cu   general-shape linear layers (any M, N, K; bf16 or fp32 storage, fp32 accumulation)
-//   recurrent.cu    short causal convolution with carried inputs, gated linear recurrences with carried fp32 state
+//   recurrent.cu    short causal convolution with carried inputs, gated linear recurrences and the gated delta rule with carried fp32 state
 //   attn_local.cu   whole-projection q/k norm + paged K/V append, chunk-local attention with a sink term
-//   rowops.cu       embedding + sinusoidal positions, post-norm residual, grouped gated RMS norm, GLU, soft cap
+//   rowops.cu       embedding + sinusoidal positions, post-norm / parallel / output-normed residual rows, grouped gated RMS norm, GLU, soft cap
 //   rotary.cu       rotate-half rotary positions on slices of a projection, packed to fp32 for a recurrence
 //   attn_latent.cu  latent (low-rank) K/V cache: latent norm + shared rotary key part -> pages, rotary query part
 //   hyper.cu        pre-norm blocks on several residual streams (hyper-connections)
-//   moe.cu          sigmoid or softmax top-k router (groups of experts, identity experts), expert row lists, weighted combine
+//   moe.cu          sigmoid, softmax or chosen-logit-softmax top-k router (groups of experts, identity experts), expert row lists, weighted combine
 // Every op exists for two storage types (DT_BF16: bf16 storage, fp32 arithmetic where the model asks for it;
 // DT_F32: everything fp32). All return 0 on success, negative on invalid arguments; launches are asynchronous on `s`.
 #pragma once

@@ -1,6 +1,6 @@
-"""Hybrid sequence models (decoder-only language models built from state-space, gated-linear-attention, chunk-local
+"""Hybrid sequence models (decoder-only language models built from state-space, gated-linear-attention, delta-rule, chunk-local
 attention, retention, latent-attention and sliding-window attention mixers, in post-norm blocks, pre-norm blocks on several
-residual streams or parallel blocks, with dense or routed feed-forwards) behind the same surface as the video-language engine: `from_pretrained`, `generate`, a cache object that
+residual streams, parallel blocks or blocks normed on the sublayer's output, with dense or routed feed-forwards) behind the same surface as the video-language engine: `from_pretrained`, `generate`, a cache object that
 callers pass back, greedy token selection in the library's sampling kernel.
 
     model = SeqLMForCausalLM.from_pretrained(path, torch_dtype="bfloat16", device_map="cuda")
@@ -8,7 +8,7 @@ callers pass back, greedy token selection in the library's sampling kernel.
     logits = model.forward_step([(cache, ids)], [[0, 2]])         # teacher-forced step: logits of chosen rows
 
 Everything numeric runs in the native library (csrc/seq_model.cu sequences one step; linear_any.cu / gemm_tcgen05.cu,
-recurrent.cu, attn_local.cu, rowops.cu hold the kernels); this file is host orchestration: weight layout, state slots and
+recurrent.cu, attn_local.cu, attn_latent.cu, moe.cu, rowops.cu hold the kernels); this file is host orchestration: weight layout, state slots and
 pages, step bookkeeping, CUDA-graph replay of the decode step. There is no CPU or eager fallback.
 
 Two storage types: bf16 (weights, activations and K/V pages in bf16; the residual stream, norms, scores, recurrent state
