@@ -260,7 +260,7 @@ __device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
 // operands of TT tokens at a time are copied into one of two shared-memory buffers with cp.async while the tokens of the
 // other buffer run, so the sequential loop reads only shared memory and registers. Per token: the state decays, the JP lanes
 // reduce St^T k and St^T q together, the write w = beta (v - St^T k) lands, and the read-out is St^T q + (k . q) w: the same
-// value as reading the state after the write, with one reduction round instead of two. Shared rows are padded to JP * NT_
+// value as reading the state after the write, with one reduction pass instead of two. Shared rows are padded to JP * NT_
 // entries and the padding stays zero, so the inner loops need no bounds.
 template <int NT_>
 __global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(DeltaScanArgs a, SeqPos pos) {
@@ -441,7 +441,7 @@ int delta_scan(const DeltaScanArgs& q, SeqPos pos, cudaStream_t s) {
         q.N < 1 || q.N > 512 || q.P < 1)
         return -2;
     DeltaScanArgs a = q;
-    // state entries per thread: 16 from 65 key channels on (8 lanes per value channel at 128: three shuffle rounds and the
+    // state entries per thread: 16 from 65 key channels on (8 lanes per value channel at 128: three shuffle steps and the
     // fewest instructions per token), fewer for narrow heads so that a channel still spreads over lanes
     static int forced = -1;
     if (forced < 0) { const char* e = getenv("LIVECC_B200_DELTA_NT"); forced = e ? atoi(e) : 0; }
