@@ -118,13 +118,13 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
     int moe_e = 0, moe_top = 0, moe_ff = 0, moe_rows = 0, moe_glu = 0;   // moe_glu: widest hidden row of a gated expert
     size_t split_floats = 0;   // key-split partials of few-row plain causal attention
     int wvk = 0;
+    size_t delta_floats = 0;   // the delta rule's prepared operands (head by head, fp32) share the fp32 query buffer
     for (const lcc_seq_layer& l : m->layers) {
         const Dims z = dims_of(l);
         if (l.type == LCC_MIX_DELTA) {
             wp = std::max(wp, z.d_proj); wm = std::max(wm, std::max(z.d_conv_ch, ld8(z.d_nv))); wp2 = std::max(wp2, ld8(z.d_nv));
             wy = std::max(wy, z.d_nv); wf = std::max(wf, l.d_heads * l.d_dim);
-            // (the head-by-head operand blocks are each padded to 4 floats: up to 5 x 4 more floats in all than rows x width)
-            wq = std::max(wq, 2 * z.d_nk + z.d_nv + l.d_kv_heads + l.d_heads + 24);
+            delta_floats = std::max(delta_floats, lcc::delta_operand_floats((int)nt, l.d_heads, l.d_kv_heads, l.d_dim, l.d_vdim));
         }
         if (l.type == LCC_MIX_LATENT && l.a_q_rank > 0) { wp2 = std::max(wp2, ld8(z.a_nq)); wm = std::max(wm, ld8(l.a_q_rank)); }
         if (l.type == LCC_MIX_ATTENTION && l.m_vmix_role == 1) wvk = std::max(wvk, ld8(z.m_nv));
@@ -186,7 +186,7 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
     L.mid = take(nt * wm * es);
     L.mid2 = take(nt * wm * es);
     L.y32 = take(nt * wy * 4);
-    L.q32 = take(nt * wq * 4);
+    L.q32 = take(std::max(nt * wq, delta_floats) * 4);
     L.f1 = take(nt * wf * 4);
     L.f2 = take(nt * wf * 4);
     L.o1 = take(nt * ld8(W) * es);
