@@ -391,8 +391,9 @@ typedef struct {
     const float* m_temp_f32;   /* [m_heads] or NULL */
     const void* a_uq;          /* [heads*(dim+rot_dim), a_q_rank] */
     const float* a_q_norm_f32; /* [a_q_rank] */
-    const void* d_in;          /* [2*G*dim + heads*vdim + heads + rank_a + rank_g, width], rows [q | k | v | beta | decay-down | gate-down] */
-    const float* d_conv_w_f32; /* [2*G*dim + heads*vdim, d_conv], rows as q, k, v */
+    const void* d_in;          /* rows [q: G*dim | k: G*dim | v: heads*vdim | beta: heads | decay-down: rank_a | gate-down: rank_g] x width,
+                                  every block padded with zero rows to a multiple of 8, so that each starts at a multiple of 8 */
+    const float* d_conv_w_f32; /* [channels, d_conv]: the q, k, v blocks of d_in with their padding (zero taps there) */
     const void* d_a_up;        /* [heads*dim, rank_a] */
     const float *d_dt_bias_f32, *d_a_log_f32; /* [heads*dim], [heads] */
     const void* d_g_up;        /* [heads*vdim, rank_g] */
@@ -462,7 +463,7 @@ typedef struct {
 
 /* One sequence's part of a step: n_new tokens that follow `past` cached ones. layer_state[i]: this sequence's fp32 state
  * slot of layer i (SSD: [conv carry: channels x (conv-1)] then [heads x vdim x state]; PARALLEL: [heads x vdim x dim] of
- * the right mixer; RETENTION: [heads x vdim x dim]; DELTA: [conv carry: channels x (conv-1)] then [heads x vdim x dim]; in a
+ * the right mixer; RETENTION: [heads x vdim x dim]; DELTA: [conv carry: (padded q, k, v channels) x (conv-1)] then [heads x vdim x dim]; in a
  * LCC_BLOCK_BRANCHNORM model every layer's slot starts with [width x (canon_taps-1)], the last inputs of the convolution in front of
  * the mixer), zero at the start of a sequence. k_pages[i] / v_pages[i]: the layer's page pools
  * [page][kv_heads][page_size][dim|vdim] (NULL for layers without attention); a LATENT layer has K pages only,
