@@ -7,6 +7,8 @@
 #include <math.h>
 #include <stdlib.h>
 
+#include <algorithm>
+
 #include "../../include/livecc_b200.h"
 #include "common.cuh"
 #include "mma.cuh"
@@ -255,22 +257,24 @@ __device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
 }
 
-// One state matrix per head; a thread keeps NT_ state entries of one value channel, JP lanes share the channel (lane j owns
-// the 4-entry groups j, j + JP, ...: neighbouring lanes read neighbouring 16-byte pieces of shared memory). The prepared
-// operands of TT tokens at a time are copied into one of two shared-memory buffers with cp.async while the tokens of the
-// other buffer run, so the sequential loop reads only shared memory and registers. Per token: the state decays, the JP lanes
-// reduce St^T k and St^T q together, the write w = beta (v - St^T k) lands, and the read-out is St^T q + (k . q) w: the same
-// value as reading the state after the write, with one reduction pass instead of two. Shared rows are padded to JP * NT_
-// entries and the padding stays zero, so the inner loops need no bounds.
-template <int NT_>
+// One state matrix per head; a thread keeps NT_ state entries of each of CPT value channels, JP lanes share those channels
+// (lane j owns the 4-entry groups j, j + JP, ...: neighbouring lanes read neighbouring 16-byte pieces of shared memory). The
+// prepared operands of TT tokens at a time are copied into one of two shared-memory buffers with cp.async while the tokens of
+// the other buffer run, so the sequential loop reads only shared memory and registers; a thread's k, q and decay entries of
+// a token are read once for its CPT channels (the kernel is bound by shared-memory reads: every channel needs the whole k, q
+// and decay rows of every token). Per token: the state decays, the JP lanes reduce St^T k and St^T q together, the write
+// w = beta (v - St^T k) lands, and the read-out is St^T q + (k . q) w: the same value as reading the state after the write,
+// with one reduction pass instead of two. Shared rows are padded to JP * NT_ entries and the padding stays zero, so the inner
+// loops need no bounds.
+template <int NT_, int CPT>
 __global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(DeltaScanArgs a, SeqPos pos) {
     if (seq_done(pos)) return;
     extern __shared__ __align__(16) float sm[];
     const int N = a.N, P = a.P, S = a.S, TTn = a.TT;
-    const int JP = blockDim.x, cols = blockDim.y;
-    const int h = blockIdx.x, col = threadIdx.y, j = threadIdx.x;
-    const int p0 = blockIdx.y * cols, p = p0 + col;
-    const int tid = threadIdx.y * JP + threadIdx.x, nthr = cols * JP;
+    const int JP = blockDim.x, groups = blockDim.y, cols = groups * CPT;      // value channels per CTA
+    const int h = blockIdx.x, j = threadIdx.x;
+    const int p0 = blockIdx.y * cols, pc = threadIdx.y * CPT, p = p0 + pc;     // the thread's first channel
+    const int tid = threadIdx.y * JP + threadIdx.x, nthr = groups * JP;
     const int NP = JP * NT_;
     const int g = h / (a.H / a.G);
     const DeltaOperands o = delta_operands(const_cast<float*>(a.ops), a.T, a.H, a.G, N, P);
@@ -285,13 +289,16 @@ __global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(DeltaScanArgs 
     for (int e = tid; e < 2 * buf_floats; e += nthr) sm[e] = 0.f;
     __syncthreads();
 
-    float2 st[NT_ / 2];          // entry i of the thread is key channel ((i / 4) * JP + j) * 4 + i % 4
-    float* gstate = a.state + ((size_t)h * P + (p < P ? p : 0)) * N;
+    float2 st[CPT][NT_ / 2];          // entry i of the thread is key channel ((i / 4) * JP + j) * 4 + i % 4
 #pragma unroll
-    for (int i = 0; i < NT_; ++i) {
-        const int n = ((i >> 2) * JP + j) * 4 + (i & 3);
-        const float v = (p < P && n < N) ? gstate[n] : 0.f;
-        if (i & 1) st[i >> 1].y = v; else st[i >> 1].x = v;
+    for (int c = 0; c < CPT; ++c) {
+        const float* gs = a.state + ((size_t)h * P + (p + c < P ? p + c : 0)) * N;
+#pragma unroll
+        for (int i = 0; i < NT_; ++i) {
+            const int n = ((i >> 2) * JP + j) * 4 + (i & 3);
+            const float v = (p + c < P && n < N) ? gs[n] : 0.f;
+            if (i & 1) st[c][i >> 1].y = v; else st[c][i >> 1].x = v;
+        }
     }
 
     auto fill = [&](int b, int t0) {
@@ -347,47 +354,66 @@ __global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(DeltaScanArgs 
         const float* sk = sm + b * buf_floats;
         const float* sq = sk + TTn * NP;
         const float* sd = sq + TTn * NP;
-        const float* su = sd + TTn * NP + col;
+        const float* su = sd + TTn * NP + pc;
         const float* sb = sd + TTn * NP + TTn * cols;
         const float* skq = sb + TTn;
         const int nt = min(TTn, S - t0);
         float* yo = a.y + (size_t)t0 * a.ld_y + (size_t)h * P + p;
-#pragma unroll 4
+#pragma unroll 2
         for (int t = 0; t < nt; ++t) {
             const float4* k4 = reinterpret_cast<const float4*>(sk + t * NP) + j;
             const float4* q4 = reinterpret_cast<const float4*>(sq + t * NP) + j;
             const float4* d4 = reinterpret_cast<const float4*>(sd + t * NP) + j;
             // packed fp32 pairs (fma.rn.f32x2: each half rounds as a scalar fma does): half the arithmetic instructions
             float2 kv[NT_ / 2];
-            float2 ks = make_float2(0.f, 0.f), qs = make_float2(0.f, 0.f);
+            float2 ks[CPT], qs[CPT];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) ks[c] = qs[c] = make_float2(0.f, 0.f);
 #pragma unroll
             for (int i = 0; i < NT_ / 4; ++i) {
                 const float4 kk = k4[i * JP], qq = q4[i * JP], dd = d4[i * JP];
                 kv[2 * i] = make_float2(kk.x, kk.y); kv[2 * i + 1] = make_float2(kk.z, kk.w);
-                st[2 * i] = __fmul2_rn(st[2 * i], make_float2(dd.x, dd.y));
-                st[2 * i + 1] = __fmul2_rn(st[2 * i + 1], make_float2(dd.z, dd.w));
-                ks = __ffma2_rn(st[2 * i], kv[2 * i], ks);
-                qs = __ffma2_rn(st[2 * i], make_float2(qq.x, qq.y), qs);
-                ks = __ffma2_rn(st[2 * i + 1], kv[2 * i + 1], ks);
-                qs = __ffma2_rn(st[2 * i + 1], make_float2(qq.z, qq.w), qs);
-            }
-            float ksum = ks.x + ks.y, qsum = qs.x + qs.y;
-            for (int o2 = JP >> 1; o2 > 0; o2 >>= 1) {          // fixed butterfly order
-                ksum += __shfl_xor_sync(0xffffffffu, ksum, o2);
-                qsum += __shfl_xor_sync(0xffffffffu, qsum, o2);
-            }
-            const float w = sb[t] * (su[t * cols] - ksum);
-            const float2 w2 = make_float2(w, w);
+                const float2 d0 = make_float2(dd.x, dd.y), d1 = make_float2(dd.z, dd.w);
+                const float2 q0 = make_float2(qq.x, qq.y), q1 = make_float2(qq.z, qq.w);
 #pragma unroll
-            for (int i = 0; i < NT_ / 2; ++i) st[i] = __ffma2_rn(kv[i], w2, st[i]);
-            if (j == 0 && p < P) yo[(size_t)t * a.ld_y] = fmaf(skq[t], w, qsum);
+                for (int c = 0; c < CPT; ++c) {
+                    st[c][2 * i] = __fmul2_rn(st[c][2 * i], d0);
+                    st[c][2 * i + 1] = __fmul2_rn(st[c][2 * i + 1], d1);
+                    ks[c] = __ffma2_rn(st[c][2 * i], kv[2 * i], ks[c]);
+                    qs[c] = __ffma2_rn(st[c][2 * i], q0, qs[c]);
+                    ks[c] = __ffma2_rn(st[c][2 * i + 1], kv[2 * i + 1], ks[c]);
+                    qs[c] = __ffma2_rn(st[c][2 * i + 1], q1, qs[c]);
+                }
+            }
+            float ksum[CPT], qsum[CPT];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) { ksum[c] = ks[c].x + ks[c].y; qsum[c] = qs[c].x + qs[c].y; }
+            for (int o2 = JP >> 1; o2 > 0; o2 >>= 1) {          // fixed butterfly order
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) {
+                    ksum[c] += __shfl_xor_sync(0xffffffffu, ksum[c], o2);
+                    qsum[c] += __shfl_xor_sync(0xffffffffu, qsum[c], o2);
+                }
+            }
+            const float beta = sb[t], kq = skq[t];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                const float w = beta * (su[t * cols + c] - ksum[c]);
+                const float2 w2 = make_float2(w, w);
+#pragma unroll
+                for (int i = 0; i < NT_ / 2; ++i) st[c][i] = __ffma2_rn(kv[i], w2, st[c][i]);
+                if (j == 0 && p + c < P) yo[(size_t)t * a.ld_y + c] = fmaf(kq, w, qsum[c]);
+            }
         }
     }
-    if (p < P) {
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        if (p + c >= P) continue;
+        float* gs = a.state + ((size_t)h * P + p + c) * N;
 #pragma unroll
         for (int i = 0; i < NT_; ++i) {
             const int n = ((i >> 2) * JP + j) * 4 + (i & 3);
-            if (n < N) gstate[n] = (i & 1) ? st[i >> 1].y : st[i >> 1].x;
+            if (n < N) gs[n] = (i & 1) ? st[c][i >> 1].y : st[c][i >> 1].x;
         }
     }
 }
@@ -441,30 +467,40 @@ int delta_scan(const DeltaScanArgs& q, SeqPos pos, cudaStream_t s) {
         q.N < 1 || q.N > 512 || q.P < 1)
         return -2;
     DeltaScanArgs a = q;
-    // state entries per thread: 16 from 65 key channels on (8 lanes per value channel at 128: three shuffle steps and the
-    // fewest instructions per token), fewer for narrow heads so that a channel still spreads over lanes
+    // state entries per thread and value channel: 8 (16 lanes per channel at 128 key channels), 16 beyond 256 key channels, 4
+    // for narrow heads so that a channel still spreads over lanes
     static int forced = -1;
     if (forced < 0) { const char* e = getenv("LIVECC_B200_DELTA_NT"); forced = e ? atoi(e) : 0; }
-    int nt = a.N > 64 ? 16 : (a.N > 16 ? 8 : 4);
+    int nt = a.N > 256 ? 16 : (a.N > 16 ? 8 : 4);
     if ((forced == 4 || forced == 8 || forced == 16) && forced * 32 >= a.N) nt = forced;
     int JP = 1;
     while (JP * nt < a.N) JP *= 2;
-    int cols = kScanThreads / JP;
-    while (cols * JP > 32 && cols / 2 >= a.P) cols /= 2;   // narrow heads: fewer idle lanes, but always whole warps
+    // value channels per thread: 2 with 8 state entries each when the head has 16 value channels or more (half the
+    // shared-memory reads per channel; measured best at 128 x 128 heads: 8 x 2 250 us, 16 x 1 310, 8 x 1 320, 16 x 2 375,
+    // 8 x 4 420 per 1024 tokens); lane groups per CTA: whole warps, 16 channels per CTA at most
+    static int forced_cpt = -1;
+    if (forced_cpt < 0) { const char* e = getenv("LIVECC_B200_DELTA_CPT"); forced_cpt = e ? atoi(e) : 0; }
+    int cpt = (nt == 8 && a.P >= 16) ? 2 : 1;
+    if (forced_cpt == 1 || forced_cpt == 2 || (forced_cpt == 4 && nt <= 8)) cpt = forced_cpt;
+    int groups = std::max(kScanThreads / JP / cpt, 32 / JP);
+    while (groups * JP > 32 && (groups / 2) * cpt >= a.P) groups /= 2;   // narrow heads: fewer idle lanes, but always whole warps
+    const int cols = groups * cpt;
     const int NP = JP * nt;
     a.TT = 16;
     while (a.TT > 2 && (size_t)2 * a.TT * (3 * NP + cols + 2) * sizeof(float) > 64 * 1024) a.TT /= 2;
     // 16-byte copies need 16-byte aligned rows in every operand block (each block starts at a multiple of 4 floats)
     a.async = (a.N % 4) == 0 && ((uintptr_t)a.ops % 16) == 0 && ((uintptr_t)a.dec % 16) == 0;
     const size_t smem = (size_t)2 * a.TT * (3 * NP + cols + 2) * sizeof(float);
-    dim3 block(JP, cols), grid(a.H, (a.P + cols - 1) / cols);
+    dim3 block(JP, groups), grid(a.H, (a.P + cols - 1) / cols);
     count_launch();
-#define LCC_DSCAN(NTV)                                                                                                          \
+#define LCC_DSCAN(NTV, CPTV)                                                                                                    \
     do {                                                                                                                        \
-        if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<NTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        delta_scan_kernel<NTV><<<grid, block, smem, s>>>(a, pos);                                                               \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<NTV, CPTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        delta_scan_kernel<NTV, CPTV><<<grid, block, smem, s>>>(a, pos);                                                         \
     } while (0)
-    if (nt == 4) LCC_DSCAN(4); else if (nt == 8) LCC_DSCAN(8); else LCC_DSCAN(16);
+    if (nt == 4) { if (cpt == 4) LCC_DSCAN(4, 4); else if (cpt == 2) LCC_DSCAN(4, 2); else LCC_DSCAN(4, 1); }
+    else if (nt == 8) { if (cpt == 4) LCC_DSCAN(8, 4); else if (cpt == 2) LCC_DSCAN(8, 2); else LCC_DSCAN(8, 1); }
+    else { if (cpt == 2) LCC_DSCAN(16, 2); else LCC_DSCAN(16, 1); }
 #undef LCC_DSCAN
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }
